@@ -1,0 +1,140 @@
+// extern "C" entry points: argument validation, kernel-family selection, error strings.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace af {
+
+static thread_local char g_error[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return AF_OK;
+  return fail(AF_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+namespace {
+
+int validate_problem(const AfProblem& p) {
+  AF_REQUIRE(p.dtype == AF_F16 || p.dtype == AF_BF16 || p.dtype == AF_F32, "unknown dtype %d", p.dtype);
+  AF_REQUIRE(p.B >= 0 && p.H_q >= 1 && p.H_kv >= 1 && p.N_q >= 0 && p.N_kv >= 0, "negative extent");
+  AF_REQUIRE(p.H_q % p.H_kv == 0, "Q heads (%d) must be a multiple of KV heads (%d)", p.H_q, p.H_kv);
+  AF_REQUIRE(p.D >= 1 && p.D <= 256, "head_dim %d outside [1, 256]", p.D);
+  AF_REQUIRE(p.mask_kind >= AF_MASK_FULL && p.mask_kind <= AF_MASK_BLOCKS, "unknown mask_kind %d", p.mask_kind);
+  AF_REQUIRE(p.bias_kind >= AF_BIAS_NONE && p.bias_kind <= AF_BIAS_ADDITIVE, "unknown bias_kind %d", p.bias_kind);
+  AF_REQUIRE(p.norm_kind == AF_NORM_SOFTMAX || p.norm_kind == AF_NORM_RELU, "unknown norm_kind %d", p.norm_kind);
+  AF_REQUIRE(p.q && p.k && p.v, "q/k/v must be non-NULL");
+  AF_REQUIRE((int64_t)p.B * p.H_q <= 65535, "B*H_q exceeds the launch grid limit");
+  if (p.mask_kind == AF_MASK_WINDOW) AF_REQUIRE(p.window > 0, "window must be positive");
+  if (p.mask_kind == AF_MASK_BLOCKS) {
+    AF_REQUIRE(p.block_m > 0 && p.block_n > 0, "block sizes must be positive");
+    AF_REQUIRE(p.kv_num && p.kv_idx, "block lists (kv_num, kv_idx) must be non-NULL");
+  }
+  if (p.bias_kind == AF_BIAS_ALIBI) AF_REQUIRE(p.slopes != nullptr, "ALiBi needs slopes");
+  if (p.bias_kind == AF_BIAS_ADDITIVE) AF_REQUIRE(p.bias != nullptr, "additive bias needs a bias tensor");
+  if (p.rope) {
+    AF_REQUIRE(p.cos && p.sin, "RoPE needs cos and sin tables");
+    AF_REQUIRE(p.D % 2 == 0, "RoPE needs an even head_dim");
+  }
+  return AF_OK;
+}
+
+}  // namespace
+}  // namespace af
+
+using namespace af;
+
+extern "C" {
+
+int af_fwd(const AfFwdParams* params, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  const AfFwdParams& a = *params;
+  int rc = validate_problem(a.p);
+  if (rc != AF_OK) return rc;
+  AF_REQUIRE(a.o != nullptr, "o must be non-NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* why = nullptr;
+  const bool tc_ok = fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why);
+  if (a.p.family == AF_FAMILY_TCGEN05) {
+    if (!tc_ok) return fail(AF_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+    return launch_fwd_tcgen05(a, st);
+  }
+  if (a.p.family == AF_FAMILY_AUTO && tc_ok) return launch_fwd_tcgen05(a, st);
+  return launch_fwd_ffma(a, st);
+}
+
+int af_bwd(const AfBwdParams* params, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  const AfBwdParams& a = *params;
+  int rc = validate_problem(a.p);
+  if (rc != AF_OK) return rc;
+  AF_REQUIRE(a.p.norm_kind == AF_NORM_SOFTMAX, "backward is defined for softmax normalisation only");
+  AF_REQUIRE(a.o && a.d_o && a.lse && a.delta && a.dq && a.dk && a.dv, "NULL backward operand");
+  if (a.p.mask_kind == AF_MASK_BLOCKS) AF_REQUIRE(a.p.q_num && a.p.q_idx, "backward needs key-major block lists");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const char* why = nullptr;
+  const bool mma_ok = bwd_mma_supports(a, &why);
+  if (a.p.family == AF_FAMILY_TCGEN05) {
+    if (!mma_ok) return fail(AF_ERR_UNSUPPORTED, "tensor-core backward: %s", why);
+    return launch_bwd_mma(a, st);
+  }
+  if (a.p.family == AF_FAMILY_AUTO && mma_ok) return launch_bwd_mma(a, st);
+  return launch_bwd_ffma(a, st);
+}
+
+int af_decode_split(const AfDecodeParams* params, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  return launch_decode_split(*params, static_cast<cudaStream_t>(stream));
+}
+
+int af_decode_combine(const AfDecodeParams* params, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  return launch_decode_combine(*params, static_cast<cudaStream_t>(stream));
+}
+
+int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int32_t H_q, int32_t D, int32_t dtype,
+                               void* o, const int64_t o_stride[4], af_stream_t stream) {
+  return launch_decode_combine_gathered(gathered, G, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));
+}
+
+int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count) {
+  // One CTA per (split, batch, kv head).  Aim for about two waves of CTAs over the SMs, keep at
+  // least 512 keys per split so the pipeline prologue amortises, cap at 64.
+  if (sm_count <= 0) sm_count = 148;
+  const int64_t units = (int64_t)(B > 0 ? B : 1) * (H_kv > 0 ? H_kv : 1);
+  int64_t want = (2LL * sm_count + units - 1) / units;
+  const int64_t cap = N_kv / 512 > 1 ? N_kv / 512 : 1;
+  if (want > cap) want = cap;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return (int32_t)want;
+}
+
+int32_t af_query_family(const AfProblem* p, int32_t backward) {
+  if (p == nullptr) return fail(AF_ERR_INVALID, "problem is NULL");
+  if (backward) {
+    AfBwdParams b{};
+    b.p = *p;
+    return bwd_mma_supports(b, nullptr) ? AF_FAMILY_TCGEN05 : AF_FAMILY_FFMA;
+  }
+  int64_t os[4] = {p->q_stride[0], p->q_stride[1], p->q_stride[2], p->q_stride[3]};
+  return fwd_tcgen05_supports(*p, p->q, os, nullptr) ? AF_FAMILY_TCGEN05 : AF_FAMILY_FFMA;
+}
+
+int64_t af_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* af_last_error(void) { return g_error; }
+int32_t af_abi_version(void) { return AF_ABI_VERSION; }
+
+}  // extern "C"

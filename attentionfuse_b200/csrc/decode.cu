@@ -1,0 +1,477 @@
+// Split-K flash-decoding for query length 1 (GQA / MQA), plus the log-sum-exp combine.
+//
+// Replaces the reference's two decode kernels (attnfuse/compiler/codegen_decode.py:46-211).
+// The work is bound by HBM: every K and V byte is read exactly once.  One CTA owns one
+// (split, batch, kv head) and serves all query heads of the group from the same K/V tiles,
+// so the cache is streamed once per group rather than once per query head.
+//
+//   * K/V tiles of 64 keys are streamed with 16-byte cp.async into a 4-stage ring in shared
+//     memory (XOR-swizzled 16-byte chunks, so ldmatrix is bank-conflict free); rows past the
+//     valid length are zero-filled by the copy itself.
+//   * The query heads of the group sit on the M side of mma.sync.m16n8k16 (padded to 16 rows,
+//     as the reference pads to BLOCK_H = 16).  For groups <= 16 the four warps split the 64
+//     keys of a tile and merge their partial (m, l, acc) at the end; for larger groups (MQA)
+//     each warp owns 16 heads and sees all keys.
+//   * Partial results go to fp32 workspaces; a vectorised combine kernel merges the splits.
+//
+// Per-sequence valid lengths (kv_lens) are an extension: the reference only has a scalar N_KV.
+#include "common.cuh"
+
+namespace af {
+namespace {
+
+constexpr int DEC_BN = 64;       // keys per pipeline stage
+constexpr int DEC_STAGES = 4;
+constexpr int DEC_THREADS = 128;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T> struct MmaOp;
+template <> struct MmaOp<__half> {
+  __device__ __forceinline__ static void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  __device__ __forceinline__ static uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct MmaOp<__nv_bfloat16> {
+  __device__ __forceinline__ static void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  __device__ __forceinline__ static uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+// Byte offset of 16-byte chunk `c` of key row `r` inside a [DEC_BN][D] tile.
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int r, int c) {
+  constexpr int ROW_BYTES = D * 2;
+  return (uint32_t)(r * ROW_BYTES + (((c & ~7) | ((c ^ r) & 7)) << 4));
+}
+
+// KPW = keys of each 64-key tile one warp handles (16: warps split keys; 64: warps split heads).
+template <typename T, int D, int KPW>
+__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks) {
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int CHUNKS = ROW_BYTES / 16;       // 16-byte chunks per row
+  constexpr int TILE_BYTES = DEC_BN * ROW_BYTES;
+  constexpr int KSTEPS = D / 16;               // k-steps of Q.K^T
+  constexpr int NT_S = KPW / 8;                // score n-tiles per warp
+  constexpr int NT_O = D / 8;                  // output n-tiles
+  constexpr bool SPLIT_KEYS = (KPW == 16);
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* sK = smem_raw;
+  unsigned char* sV = smem_raw + DEC_STAGES * TILE_BYTES;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x;
+  int bid = blockIdx.y;
+  const int chunk = bid % head_chunks; bid /= head_chunks;
+  const int h_kv = bid % a.H_kv;
+  const int b = bid / a.H_kv;
+  const int group = a.H_q / a.H_kv;
+  // First head (inside the group) of this warp's 16-row M tile.
+  const int head0 = chunk * 64 + (SPLIT_KEYS ? 0 : warp * 16);
+  const int key_w0 = SPLIT_KEYS ? warp * 16 : 0;   // first key of the tile this warp handles
+
+  const int len_b = a.kv_lens ? min(max(a.kv_lens[b], 0), a.N_kv) : a.N_kv;
+  int split_len = (len_b + a.num_splits - 1) / a.num_splits;
+  split_len = ((split_len + DEC_BN - 1) / DEC_BN) * DEC_BN;
+  const int lo = split * split_len;
+  const int hi = min(lo + split_len, len_b);
+  const int n_tiles = hi > lo ? (hi - lo + DEC_BN - 1) / DEC_BN : 0;
+
+  const T* kbase = reinterpret_cast<const T*>(a.k) + (int64_t)b * a.k_stride[0] + (int64_t)h_kv * a.k_stride[1];
+  const T* vbase = reinterpret_cast<const T*>(a.v) + (int64_t)b * a.v_stride[0] + (int64_t)h_kv * a.v_stride[1];
+
+  auto issue = [&](int tile, int slot) {
+    const int key0 = lo + tile * DEC_BN;
+    for (int i = tid; i < DEC_BN * CHUNKS; i += DEC_THREADS) {
+      const int r = i / CHUNKS, c = i - r * CHUNKS;
+      const int key = key0 + r;
+      const bool ok = key < hi;
+      const int64_t krow = ok ? key : 0;
+      const uint32_t off = tile_off<D>(r, c);
+      cp_async16(smem_u32(sK + slot * TILE_BYTES + off), kbase + krow * a.k_stride[2] + c * 8, ok ? 16 : 0);
+      cp_async16(smem_u32(sV + slot * TILE_BYTES + off), vbase + krow * a.v_stride[2] + c * 8, ok ? 16 : 0);
+    }
+  };
+
+  // Query fragments: rows g and g+8 of the M tile; rows past the group are zero.
+  uint32_t qf[KSTEPS][4];
+  {
+    const int hl0 = head0 + g, hl1 = head0 + g + 8;
+    const bool ok0 = hl0 < group, ok1 = hl1 < group;
+    const T* q0 = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_stride[0] +
+                  (int64_t)(h_kv * group + (ok0 ? hl0 : 0)) * a.q_stride[1];
+    const T* q1 = reinterpret_cast<const T*>(a.q) + (int64_t)b * a.q_stride[0] +
+                  (int64_t)(h_kv * group + (ok1 ? hl1 : 0)) * a.q_stride[1];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int d = kk * 16 + 2 * t;
+      qf[kk][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+      qf[kk][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+      qf[kk][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+      qf[kk][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+    }
+  }
+
+  const float scale2 = a.sm_scale * kLog2e;
+  float slope2[2] = {0.f, 0.f};
+  if (a.bias_kind == AF_BIAS_ALIBI) {
+    const int hl0 = head0 + g, hl1 = head0 + g + 8;
+    if (hl0 < group) slope2[0] = load_slope<T>(a.slopes, h_kv * group + hl0) * kLog2e;
+    if (hl1 < group) slope2[1] = load_slope<T>(a.slopes, h_kv * group + hl1) * kLog2e;
+  }
+  // ALiBi distance is measured from the query position: the last valid key
+  // (attnfuse/compiler/codegen_decode.py:142-145 uses N_KV - 1).
+  const int q_pos = a.q_positions ? a.q_positions[b] : (a.kv_offset + len_b - 1);
+
+  float m2[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT_O][4];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_tiles) issue(s, s);
+    cp_async_commit();
+  }
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = tile + DEC_STAGES - 1;
+      if (nxt < n_tiles) issue(nxt, nxt % DEC_STAGES);
+      cp_async_commit();
+    }
+    const int slot = tile % DEC_STAGES;
+    const uint32_t kt = smem_u32(sK + slot * TILE_BYTES);
+    const uint32_t vt = smem_u32(sV + slot * TILE_BYTES);
+    const int key_base = lo + tile * DEC_BN + key_w0;   // first key this warp sees in the tile
+    if (SPLIT_KEYS && key_base >= hi) continue;         // warp-uniform: nothing valid here
+
+    // ---- S = Q K^T ------------------------------------------------------------------
+    float s[NT_S][4];
+#pragma unroll
+    for (int j = 0; j < NT_S; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+      for (int jp = 0; jp < NT_S / 2; ++jp) {
+        // matrices: (keys 0-7, chunk 2kk) (keys 0-7, chunk 2kk+1) (keys 8-15, 2kk) (keys 8-15, 2kk+1)
+        const int r = key_w0 + jp * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int c = 2 * kk + ((lane >> 3) & 1);
+        uint32_t bf[4];
+        ldmatrix_x4(bf, kt + tile_off<D>(r, c));
+        MmaOp<T>::run(s[2 * jp], qf[kk], bf[0], bf[1]);
+        MmaOp<T>::run(s[2 * jp + 1], qf[kk], bf[2], bf[3]);
+      }
+    }
+
+    // ---- online softmax (base 2) ----------------------------------------------------
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NT_S; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key_base + j * 8 + 2 * t + (e & 1);
+        const int row = e >> 1;
+        float x = s[j][e] * scale2;
+        if (a.bias_kind == AF_BIAS_ALIBI) x -= slope2[row] * (float)abs(q_pos - (a.kv_offset + key));
+        x = key < hi ? x : -INFINITY;
+        s[j][e] = x;
+        mx[row] = fmaxf(mx[row], x);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+      mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 1));
+      mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 2));
+      const float m_new = fmaxf(m2[row], mx[row]);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[row] = exp2f(m2[row] - m_use);
+      m2[row] = m_new;
+      mx[row] = m_use;
+    }
+    float rs[2] = {0.f, 0.f};
+    uint32_t pf[NT_S][2];
+#pragma unroll
+    for (int j = 0; j < NT_S; ++j) {
+      const float p0 = exp2f(s[j][0] - mx[0]), p1 = exp2f(s[j][1] - mx[0]);
+      const float p2 = exp2f(s[j][2] - mx[1]), p3 = exp2f(s[j][3] - mx[1]);
+      rs[0] += p0 + p1;
+      rs[1] += p2 + p3;
+      pf[j][0] = MmaOp<T>::pack(p0, p1);
+      pf[j][1] = MmaOp<T>::pack(p2, p3);
+    }
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+      rs[row] += __shfl_xor_sync(0xffffffffu, rs[row], 1);
+      rs[row] += __shfl_xor_sync(0xffffffffu, rs[row], 2);
+      l[row] = l[row] * alpha[row] + rs[row];
+    }
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+
+    // ---- O += P V -------------------------------------------------------------------
+#pragma unroll
+    for (int ks = 0; ks < KPW / 16; ++ks) {
+      const uint32_t af[4] = {pf[2 * ks][0], pf[2 * ks][1], pf[2 * ks + 1][0], pf[2 * ks + 1][1]};
+#pragma unroll
+      for (int dp = 0; dp < NT_O / 2; ++dp) {
+        // matrices: (keys 0-7, chunk dp*2) (keys 8-15, chunk dp*2) (keys 0-7, dp*2+1) (keys 8-15, dp*2+1)
+        const int r = key_w0 + ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int c = 2 * dp + (lane >> 4);
+        uint32_t bf[4];
+        ldmatrix_x4_trans(bf, vt + tile_off<D>(r, c));
+        MmaOp<T>::run(o[2 * dp], af, bf[0], bf[1]);
+        MmaOp<T>::run(o[2 * dp + 1], af, bf[2], bf[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const int64_t ws_row0 = ((int64_t)split * a.B + b) * a.H_q + (int64_t)h_kv * group;
+  if (SPLIT_KEYS) {
+    // Merge the four warps' partials (each saw a quarter of the keys) through shared memory.
+    float* sm_m = reinterpret_cast<float*>(smem_raw);        // [4][16]
+    float* sm_l = sm_m + 64;                                 // [4][16]
+    float* sm_o = sm_l + 64;                                 // [4][16][D]
+    if (t == 0) {
+      sm_m[warp * 16 + g] = m2[0]; sm_m[warp * 16 + g + 8] = m2[1];
+      sm_l[warp * 16 + g] = l[0];  sm_l[warp * 16 + g + 8] = l[1];
+    }
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      float* r0 = sm_o + ((warp * 16 + g) * D) + i * 8 + 2 * t;
+      float* r1 = sm_o + ((warp * 16 + g + 8) * D) + i * 8 + 2 * t;
+      r0[0] = o[i][0]; r0[1] = o[i][1];
+      r1[0] = o[i][2]; r1[1] = o[i][3];
+    }
+    __syncthreads();
+    const int rows = min(group - head0, 16);
+    for (int idx = tid; idx < rows * D; idx += DEC_THREADS) {
+      const int r = idx / D, d = idx - r * D;
+      float mstar = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mstar = fmaxf(mstar, sm_m[w * 16 + r]);
+      const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+      float acc = 0.f, lsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float sc = exp2f(sm_m[w * 16 + r] - m_use);
+        acc += sc * sm_o[(w * 16 + r) * D + d];
+        lsum += sc * sm_l[w * 16 + r];
+      }
+      const int64_t row = ws_row0 + head0 + r;
+      a.ws_acc[row * D + d] = acc;
+      if (d == 0) {
+        a.ws_m[row] = mstar * kLn2;
+        a.ws_l[row] = lsum;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+      const int hl = head0 + g + 8 * row;
+      if (hl >= group) continue;
+      const int64_t wr = ws_row0 + hl;
+      if (t == 0) {
+        a.ws_m[wr] = m2[row] * kLn2;
+        a.ws_l[wr] = l[row];
+      }
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i)
+        *reinterpret_cast<float2*>(a.ws_acc + wr * D + i * 8 + 2 * t) =
+            make_float2(o[i][2 * row], o[i][2 * row + 1]);
+    }
+  }
+}
+
+// Merge the per-split partials of one (batch, head) row: one warp per row, float4 lanes.
+// Reference: attnfuse/compiler/codegen_decode.py:172-211.
+template <typename T, int D>
+__global__ void decode_combine_kernel(const AfDecodeParams a) {
+  constexpr int VEC = D / 32;   // floats per lane: 2 (D=64) or 4 (D=128)
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int rows = a.B * a.H_q;
+  if (row >= rows) return;
+  const int S = a.num_splits;
+  float mstar = -INFINITY;
+  for (int s = 0; s < S; ++s) mstar = fmaxf(mstar, a.ws_m[(int64_t)s * rows + row]);
+  const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+  float acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  float lsum = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const int64_t r = (int64_t)s * rows + row;
+    const float w = expf(a.ws_m[r] - m_use);
+    lsum += w * a.ws_l[r];
+    const float* src = a.ws_acc + r * D + lane * VEC;
+    if constexpr (VEC == 4) {
+      const float4 x = *reinterpret_cast<const float4*>(src);
+      acc[0] += w * x.x; acc[1] += w * x.y; acc[2] += w * x.z; acc[3] += w * x.w;
+    } else {
+      const float2 x = *reinterpret_cast<const float2*>(src);
+      acc[0] += w * x.x; acc[1] += w * x.y;
+    }
+  }
+  const float inv = lsum == 0.f ? 0.f : 1.f / lsum;
+  const int b = row / a.H_q, h = row % a.H_q;
+  if (a.o != nullptr) {
+    T* dst = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) dst[(int64_t)(lane * VEC + i) * a.o_stride[3]] = Elem<T>::from_f32(acc[i] * inv);
+  }
+  if (a.partial != nullptr) {
+    float* dst = a.partial + (int64_t)row * (D + 1);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) dst[lane * VEC + i] = acc[i] * inv;
+    if (lane == 0) dst[D] = lsum == 0.f ? -INFINITY : mstar + logf(lsum);
+  }
+}
+
+// Merge G per-rank partials laid out [G][rows][D+1] (normalised O, then LSE).
+template <typename T>
+__global__ void decode_combine_gathered_kernel(const float* __restrict__ gathered, int G, int rows, int H_q,
+                                               int D, T* o, int64_t s0, int64_t s1, int64_t s3) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int64_t stride_g = (int64_t)rows * (D + 1);
+  float mstar = -INFINITY;
+  for (int r = 0; r < G; ++r) mstar = fmaxf(mstar, gathered[r * stride_g + (int64_t)row * (D + 1) + D]);
+  const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+  float wsum = 0.f;
+  for (int r = 0; r < G; ++r) wsum += expf(gathered[r * stride_g + (int64_t)row * (D + 1) + D] - m_use);
+  const float inv = (mstar == -INFINITY) ? 0.f : 1.f / wsum;
+  T* dst = o + (int64_t)(row / H_q) * s0 + (int64_t)(row % H_q) * s1;
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int r = 0; r < G; ++r) {
+      const float* src = gathered + r * stride_g + (int64_t)row * (D + 1);
+      const float lse = src[D];
+      if (lse != -INFINITY) acc += expf(lse - m_use) * src[d];
+    }
+    dst[(int64_t)d * s3] = Elem<T>::from_f32(acc * inv);
+  }
+}
+
+template <typename T, int D>
+int launch_split_impl(const AfDecodeParams& a, cudaStream_t st) {
+  const int group = a.H_q / a.H_kv;
+  const int head_chunks = (group + 63) / 64;
+  const size_t smem = (size_t)2 * DEC_STAGES * DEC_BN * D * 2;
+  dim3 grid(a.num_splits, a.B * a.H_kv * head_chunks);
+  if (group <= 16) {
+    auto kern = decode_split_kernel<T, D, 16>;
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);
+  } else {
+    auto kern = decode_split_kernel<T, D, 64>;
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);
+  }
+  count_launch();
+  return check_cuda(cudaGetLastError(), "decode_split launch");
+}
+
+template <typename T, int D>
+int launch_combine_impl(const AfDecodeParams& a, cudaStream_t st) {
+  const int rows = a.B * a.H_q;
+  decode_combine_kernel<T, D><<<(rows + 3) / 4, 128, 0, st>>>(a);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "decode_combine launch");
+}
+
+int validate_decode(const AfDecodeParams& a) {
+  AF_REQUIRE(a.dtype == AF_F16 || a.dtype == AF_BF16, "decode kernels take f16/bf16 (got dtype %d)", a.dtype);
+  AF_REQUIRE(a.D == 64 || a.D == 128, "decode kernels are instantiated for D in {64,128} (got %d)", a.D);
+  AF_REQUIRE(a.B > 0 && a.H_kv > 0 && a.H_q > 0 && a.H_q % a.H_kv == 0, "bad head/batch counts");
+  AF_REQUIRE(a.num_splits >= 1, "num_splits must be >= 1");
+  AF_REQUIRE((int64_t)a.B * a.H_kv * ((a.H_q / a.H_kv + 63) / 64) <= 65535, "B*H_kv too large for one launch");
+  AF_REQUIRE(a.ws_m && a.ws_l && a.ws_acc, "decode workspaces must be non-NULL");
+  return AF_OK;
+}
+
+}  // namespace
+
+int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
+  int rc = validate_decode(a);
+  if (rc != AF_OK) return rc;
+  AF_REQUIRE(a.q && a.k && a.v, "q/k/v must be non-NULL");
+  AF_REQUIRE(a.q_stride[3] == 1 && a.k_stride[3] == 1 && a.v_stride[3] == 1, "decode needs unit inner strides");
+  AF_REQUIRE(a.k_stride[2] % 8 == 0 && a.v_stride[2] % 8 == 0 && a.k_stride[1] % 8 == 0 && a.v_stride[1] % 8 == 0 &&
+                 a.k_stride[0] % 8 == 0 && a.v_stride[0] % 8 == 0,
+             "decode needs 16-byte aligned K/V rows");
+  AF_REQUIRE(((uintptr_t)a.k % 16) == 0 && ((uintptr_t)a.v % 16) == 0 && ((uintptr_t)a.q % 4) == 0,
+             "decode needs 16-byte aligned K/V base pointers");
+  AF_REQUIRE(a.q_stride[1] % 2 == 0 && a.q_stride[0] % 2 == 0, "decode needs 4-byte aligned Q rows");
+  AF_REQUIRE(a.bias_kind == AF_BIAS_NONE || (a.bias_kind == AF_BIAS_ALIBI && a.slopes), "bad bias_kind for decode");
+  if (a.dtype == AF_F16) return a.D == 64 ? launch_split_impl<__half, 64>(a, st) : launch_split_impl<__half, 128>(a, st);
+  return a.D == 64 ? launch_split_impl<__nv_bfloat16, 64>(a, st) : launch_split_impl<__nv_bfloat16, 128>(a, st);
+}
+
+int launch_decode_combine(const AfDecodeParams& a, cudaStream_t st) {
+  int rc = validate_decode(a);
+  if (rc != AF_OK) return rc;
+  AF_REQUIRE(a.o || a.partial, "combine needs o or partial");
+  if (a.dtype == AF_F16) return a.D == 64 ? launch_combine_impl<__half, 64>(a, st) : launch_combine_impl<__half, 128>(a, st);
+  return a.D == 64 ? launch_combine_impl<__nv_bfloat16, 64>(a, st) : launch_combine_impl<__nv_bfloat16, 128>(a, st);
+}
+
+int launch_decode_combine_gathered(const float* gathered, int G, int B, int H_q, int D, int dtype, void* o,
+                                   const int64_t* os, cudaStream_t st) {
+  AF_REQUIRE(gathered && o && os, "NULL argument");
+  AF_REQUIRE(G >= 1 && B >= 1 && H_q >= 1 && D >= 1, "bad sizes");
+  const int rows = B * H_q;
+  const unsigned blocks = (rows + 3) / 4;
+  if (dtype == AF_F16)
+    decode_combine_gathered_kernel<__half><<<blocks, 128, 0, st>>>(gathered, G, rows, H_q, D, (__half*)o, os[0], os[1], os[3]);
+  else if (dtype == AF_BF16)
+    decode_combine_gathered_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(gathered, G, rows, H_q, D, (__nv_bfloat16*)o, os[0], os[1], os[3]);
+  else if (dtype == AF_F32)
+    decode_combine_gathered_kernel<float><<<blocks, 128, 0, st>>>(gathered, G, rows, H_q, D, (float*)o, os[0], os[1], os[3]);
+  else
+    return fail(AF_ERR_INVALID, "unknown dtype %d", dtype);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "decode_combine_gathered launch");
+}
+
+}  // namespace af

@@ -1,0 +1,566 @@
+// Forward attention on the 5th-generation tensor cores (tcgen05 + TMEM) with TMA staging.
+//
+// Replaces the reference forward kernel (attnfuse/compiler/codegen.py:67-381) and its
+// block-sparse sibling (attnfuse/compiler/codegen_blocksparse.py:34-171) for f16/bf16 inputs
+// with head_dim 64 or 128 and softmax normalisation.
+//
+// One CTA owns 128 query rows of one (batch, query head) and walks 128-key tiles:
+//
+//   producer warp   TMA loads: the Q tile once, then K and V tiles into a STAGES-deep ring of
+//                   128-byte-swizzled shared-memory tiles (no cluster multicast anywhere).
+//   rotation group  (RoPE only) two warps rotate each K tile in place in shared memory as it
+//                   lands -- fp32 math, rounded back to the input dtype exactly as the reference
+//                   does before its dot (codegen.py:332-341) -- then hand it to the MMA warp.
+//                   The Q tile is rotated once by the softmax group (codegen.py:126-135).
+//   MMA warp        one thread issues  S = Q K^T  (tcgen05.mma, operands from shared memory,
+//                   fp32 accumulator in TMEM, two S buffers) and  O += P V  (P read from TMEM,
+//                   V from shared memory, N-major), and commits to mbarriers.
+//   softmax group   128 threads, one query row each (TMEM lane = row, so row max / row sum need
+//                   no shuffles): tcgen05.ld the S row, apply scale, ALiBi, causal / window /
+//                   length masks, online softmax in base 2, write P as f16/bf16 over the S
+//                   buffer with tcgen05.st.  O stays in TMEM; it is rescaled only when a row max
+//                   grew by more than 2^8 since the value the accumulator is expressed in
+//                   (the result is mathematically unchanged: P, l and O share that reference).
+//
+// Every mbarrier wait is bounded; on a timeout the CTA raises a status word, drains and
+// frees its TMEM.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace af {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int PANEL_BYTES = 128 * 128;   // 128 rows x 64 elements x 2 bytes
+constexpr float kRescaleThreshold = 8.f; // log2 units
+
+template <int D> struct Cfg {
+  static constexpr int PANELS = D / 64;
+  static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;     // one Q, K or V tile
+  static constexpr int STAGES = (D == 128) ? 3 : 4;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+};
+
+struct Barriers {
+  uint64_t q_full, q_ready;
+  uint64_t k_full[4], k_ready[4], k_empty[4];
+  uint64_t v_full[4], v_empty[4];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct TcArgs {
+  AfFwdParams a;
+  int num_m_blocks;
+  int kv_tiles_per_block;   // block_n / 128 for block lists
+  int q_tiles_per_block;    // block_m / 128
+};
+
+// Which key tiles a query tile visits.
+struct TileWalk {
+  int n_tiles;
+  int first_tile;            // dense / causal / window: tile index of step 0
+  const int32_t* list;       // block lists: active key blocks of this query block
+  int per_block;
+  __device__ __forceinline__ int key0(int j) const {
+    if (list != nullptr) return (list[j / per_block] * per_block + (j % per_block)) * BN;
+    return (first_tile + j) * BN;
+  }
+};
+
+__device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& args, int m_blk, int h) {
+  TileWalk w;
+  w.list = nullptr;
+  w.per_block = 1;
+  w.first_tile = 0;
+  const int m0 = m_blk * BM;
+  const int m_end = min(m0 + BM, p.N_q);
+  if (p.mask_kind == AF_MASK_BLOCKS) {
+    const int qb = m_blk / args.q_tiles_per_block;
+    w.per_block = args.kv_tiles_per_block;
+    w.list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q;
+    w.n_tiles = p.kv_num[(int64_t)h * p.kv_num_stride_h + qb] * w.per_block;
+  } else if (p.mask_kind == AF_MASK_CAUSAL) {
+    w.n_tiles = (min(m_end, p.N_kv) + BN - 1) / BN;
+  } else if (p.mask_kind == AF_MASK_WINDOW) {
+    const int lo = max(0, m0 - p.window + 1);
+    const int hi = min(p.N_kv, m_end + p.window - 1);
+    w.first_tile = lo / BN;
+    w.n_tiles = hi > lo ? (hi + BN - 1) / BN - w.first_tile : 0;
+  } else {
+    w.n_tiles = (p.N_kv + BN - 1) / BN;
+  }
+  if (w.n_tiles < 0) w.n_tiles = 0;
+  return w;
+}
+
+template <typename T> struct Pack2;
+template <> struct Pack2<__half> {
+  __device__ __forceinline__ static uint32_t run(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static float2 unpack(uint32_t x) {
+    return __half22float2(*reinterpret_cast<__half2*>(&x));
+  }
+};
+template <> struct Pack2<__nv_bfloat16> {
+  __device__ __forceinline__ static uint32_t run(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __device__ __forceinline__ static float2 unpack(uint32_t x) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&x));
+  }
+};
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Rotate-half on row `r` of a 128-row tile stored as 64-element panels with the 128-byte TMA
+// swizzle (16-byte chunk c of row r lives at chunk c ^ (r & 7)).  Element d pairs with
+// d + D/2: the same chunk of the second panel for D = 128, chunk c + 4 of the same panel for
+// D = 64.  fp32 math, one rounding to T.
+template <typename T, int D>
+__device__ __forceinline__ void rope_row(uint32_t tile, int r, const T* cos_row, const T* sin_row) {
+  constexpr int HC = D / 16;  // 16-byte chunks per half row
+  const uint32_t row_base = tile + r * 128;
+#pragma unroll
+  for (int c = 0; c < HC; ++c) {
+    const uint32_t a_lo = row_base + ((c ^ (r & 7)) << 4);
+    const uint32_t a_hi = (D == 128) ? a_lo + PANEL_BYTES : row_base + (((c + HC) ^ (r & 7)) << 4);
+    const uint4 xl = lds128(a_lo), xh = lds128(a_hi);
+    const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_row + c * 8));
+    const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_row + D / 2 + c * 8));
+    const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_row + c * 8));
+    const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_row + D / 2 + c * 8));
+    const uint32_t xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
+    const uint32_t clw[4] = {cl.x, cl.y, cl.z, cl.w}, chw[4] = {ch.x, ch.y, ch.z, ch.w};
+    const uint32_t slw[4] = {sl.x, sl.y, sl.z, sl.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+    uint32_t ol[4], oh[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x1 = Pack2<T>::unpack(xlw[i]), x2 = Pack2<T>::unpack(xhw[i]);
+      const float2 c1 = Pack2<T>::unpack(clw[i]), c2 = Pack2<T>::unpack(chw[i]);
+      const float2 s1 = Pack2<T>::unpack(slw[i]), s2 = Pack2<T>::unpack(shw[i]);
+      ol[i] = Pack2<T>::run(x1.x * c1.x - x2.x * s1.x, x1.y * c1.y - x2.y * s1.y);
+      oh[i] = Pack2<T>::run(x2.x * c2.x + x1.x * s2.x, x2.y * c2.y + x1.y * s2.y);
+    }
+    sts128(a_lo, make_uint4(ol[0], ol[1], ol[2], ol[3]));
+    sts128(a_hi, make_uint4(oh[0], oh[1], oh[2], oh[3]));
+  }
+}
+
+template <typename T, int D, bool ROPE>
+__global__ void __launch_bounds__(ROPE ? 256 : 192, 1)
+fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
+  using C = Cfg<D>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int AB_FMT = (Elem<T>::code == AF_BF16) ? 1 : 0;
+  constexpr uint32_t IDESC_QK = umma_idesc_f16(AB_FMT, BM, BN, 0, 0);
+  constexpr uint32_t IDESC_PV = umma_idesc_f16(AB_FMT, BM, D, 0, 1);
+
+  const AfFwdParams& a = args.a;
+  const AfProblem& p = a.p;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base;
+  const uint32_t sK0 = sQ + C::TILE_BYTES;
+  const uint32_t sV0 = sK0 + STAGES * C::TILE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::TILE_BYTES * (1 + 2 * STAGES));
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // Tile assignment: the heaviest query tiles (causal: the last ones) are issued first.
+  const int bh_count = p.B * p.H_q;
+  const int m_blk = (p.mask_kind == AF_MASK_CAUSAL) ? (args.num_m_blocks - 1 - (int)(blockIdx.x / bh_count))
+                                                    : (int)(blockIdx.x / bh_count);
+  const int bh = blockIdx.x % bh_count;
+  const int b = bh / p.H_q, h = bh % p.H_q;
+  const int h_kv = h / (p.H_q / p.H_kv);
+  const int m0 = m_blk * BM;
+  const TileWalk walk = make_walk(p, args, m_blk, h);
+  const int n_tiles = walk.n_tiles;
+
+  if (tid == 0) {
+    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_ready, 128);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_ready[s], 64);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->pv_done[t], 1);
+    }
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 4) {
+    // ============================== TMA producer ==============================
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < C::PANELS; ++pn)
+        tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, m0, h, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % STAGES;
+        const uint32_t par = ((j / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
+        const int key0 = walk.key0(j);
+        unsigned char* dk = smem + C::TILE_BYTES * (1 + s);
+        unsigned char* dv = smem + C::TILE_BYTES * (1 + STAGES + s);
+        if (j >= STAGES && !mbar_wait(&bars->k_empty[s], par, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < C::PANELS; ++pn)
+          tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, h_kv, b);
+        if (j >= STAGES && !mbar_wait(&bars->v_empty[s], par, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < C::PANELS; ++pn)
+          tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, h_kv, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ============================== MMA issuer ==============================
+    if (lane == 0 && n_tiles > 0) {
+      bool ok = mbar_wait(ROPE ? &bars->q_ready : &bars->q_full, 0, abort_flag);
+      tc_fence_after_sync();
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % STAGES, t = j & 1;
+        if (!mbar_wait(ROPE ? &bars->k_ready[s] : &bars->k_full[s], (j / STAGES) & 1, abort_flag)) return false;
+        if (j >= 2 && !mbar_wait(&bars->pv_done[t], ((j >> 1) - 1) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
+        const uint32_t kbase = sK0 + s * C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
+          umma_ss(d_tmem, umma_desc_sw128(sQ + off, 16, 1024), umma_desc_sw128(kbase + off, 16, 1024), IDESC_QK,
+                  kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->k_empty[s]);
+        umma_commit(&bars->s_full[t]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int s = j % STAGES, t = j & 1;
+        if (!mbar_wait(&bars->v_full[s], (j / STAGES) & 1, abort_flag)) break;
+        if (!mbar_wait(&bars->p_full[t], (j >> 1) & 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
+        const uint32_t vbase = sV0 + s * C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns of
+          // D live one panel further (LBO).
+          umma_ts(tmem + C::COL_O, p_tmem + kk * 8, umma_desc_sw128(vbase + kk * 2048, PANEL_BYTES, 1024), IDESC_PV,
+                  (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->v_empty[s]);
+        umma_commit(&bars->pv_done[t]);
+      }
+    }
+  } else if (warp < 4) {
+    // ============================== softmax / epilogue ==============================
+    const int row = m0 + tid;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    if (ROPE && n_tiles > 0) {
+      if (mbar_wait(&bars->q_full, 0, abort_flag)) {
+        if (row < p.N_q)
+          rope_row<T, D>(sQ, tid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
+                         reinterpret_cast<const T*>(p.sin) + (int64_t)row * p.rope_stride_n);
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->q_ready);
+      }
+    }
+    const float scale2 = p.sm_scale * kLog2e;
+    const float slope2 = (p.bias_kind == AF_BIAS_ALIBI) ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool alive = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      const int t = j & 1;
+      const int key0 = walk.key0(j);
+      if (!mbar_wait(&bars->s_full[t], (j >> 1) & 1, abort_flag)) { alive = false; break; }
+      tc_fence_after_sync();
+      const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
+      uint32_t xr[BN];   // fp32 bit patterns of this row's scores
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, &xr[c * 32]);
+      tmem_wait_ld();
+
+      bool need_mask = key0 + BN > p.N_kv;
+      if (p.mask_kind == AF_MASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
+      if (p.mask_kind == AF_MASK_WINDOW)
+        need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
+
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) {
+        float v = __uint_as_float(xr[c]) * scale2;
+        if (p.bias_kind == AF_BIAS_ALIBI) v -= slope2 * (float)abs(row - (key0 + c));
+        if (need_mask) {
+          const int key = key0 + c;
+          bool keep = key < p.N_kv;
+          if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (row >= key);
+          if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(row - key) < p.window);
+          v = keep ? v : -INFINITY;
+        }
+        xr[c] = __float_as_uint(v);
+        mx = fmaxf(mx, v);
+      }
+      const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
+      const float m_next = bump ? mx : m_ref;
+      const float alpha = bump ? exp2f(m_ref - m_next) : 1.f;
+      m_ref = m_next;
+      const float m_use = (m_next == -INFINITY) ? 0.f : m_next;
+
+      if (j > 0 && __any_sync(0xffffffffu, bump)) {
+        // The accumulator is expressed relative to the old reference: rescale it in TMEM once
+        // the previous P.V product has landed.
+        if (!mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+
+      float rs = 0.f;
+      uint32_t pk[BN / 2];
+#pragma unroll
+      for (int c = 0; c < BN; c += 2) {
+        const float p0 = exp2f(__uint_as_float(xr[c]) - m_use), p1 = exp2f(__uint_as_float(xr[c + 1]) - m_use);
+        rs += p0 + p1;
+        pk[c >> 1] = Pack2<T>::run(p0, p1);
+      }
+      l_sum = l_sum * alpha + rs;
+      tmem_st32(s_tmem, &pk[0]);
+      tmem_st32(s_tmem + 32, &pk[32]);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full[t]);
+    }
+
+    // Epilogue: O / l, store row; L = m + log(l).
+    if (alive && n_tiles > 0) {
+      const int jl = n_tiles - 1;
+      alive = mbar_wait(&bars->pv_done[jl & 1], (jl >> 1) & 1, abort_flag);
+      tc_fence_after_sync();
+    }
+    if (alive) {
+      const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
+      const float inv = 1.f / safe_l;
+      T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +
+                (int64_t)row * a.o_stride[2];
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row < p.N_q) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 v;
+            v.x = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
+            v.y = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
+            v.z = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
+            v.w = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
+          }
+        }
+      }
+      if (a.lse != nullptr && row < p.N_q)
+        a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
+            m_ref * kLn2 + logf(safe_l);
+    }
+  } else if (ROPE && warp >= 6) {
+    // ============================== K rotation group ==============================
+    // Two warps (eight warps per CTA keep 255 registers per thread available to the softmax
+    // group); each thread rotates two key rows of the tile.
+    const int r0 = tid - 192;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j % STAGES;
+      if (!mbar_wait(&bars->k_full[s], (j / STAGES) & 1, abort_flag)) break;
+      const int key0 = walk.key0(j);
+#pragma unroll 1
+      for (int r = r0; r < BN; r += 64) {
+        const int pos = key0 + r;
+        if (pos < p.N_kv)
+          rope_row<T, D>(sK0 + s * C::TILE_BYTES, r,
+                         reinterpret_cast<const T*>(p.cos) + (int64_t)pos * p.rope_stride_n,
+                         reinterpret_cast<const T*>(p.sin) + (int64_t)pos * p.rope_stride_n);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->k_ready[s]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, AF_STATUS_WAIT_TIMEOUT);
+  if (warp == 4) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x 128 x 1 x 1.
+int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t esz = 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  // Strides of extent-1 dimensions are never used for addressing; give them a legal value.
+  cuuint64_t sN = (cuuint64_t)st[2] * esz, sH = (cuuint64_t)st[1] * esz, sB = (cuuint64_t)st[0] * esz;
+  if (N == 1) sN = (cuuint64_t)D * esz;
+  if (H == 1) sH = sN * (cuuint64_t)N;
+  if (B == 1) sB = sH * (cuuint64_t)H;
+  cuuint64_t strides[3] = {sN, sH, sB};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, dtype == AF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return AF_OK;
+}
+
+bool tma_ok(const void* ptr, int B, int H, int N, const int64_t* st) {
+  if (((uintptr_t)ptr & 15) != 0 || st[3] != 1) return false;
+  if (N > 1 && (st[2] <= 0 || st[2] % 8 != 0)) return false;
+  if (H > 1 && (st[1] <= 0 || st[1] % 8 != 0)) return false;
+  if (B > 1 && (st[0] <= 0 || st[0] % 8 != 0)) return false;
+  return true;
+}
+
+template <typename T, int D, bool ROPE>
+int launch_impl(const AfFwdParams& a, cudaStream_t st) {
+  const AfProblem& p = a.p;
+  TcArgs args;
+  args.a = a;
+  args.num_m_blocks = (p.N_q + BM - 1) / BM;
+  args.kv_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_n / BN : 1;
+  args.q_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_m / BM : 1;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, p.dtype, p.q, p.B, p.H_q, p.N_q, D, p.q_stride)) != AF_OK) return rc;
+  if ((rc = make_map(&mk, p.dtype, p.k, p.B, p.H_kv, p.N_kv, D, p.k_stride)) != AF_OK) return rc;
+  if ((rc = make_map(&mv, p.dtype, p.v, p.B, p.H_kv, p.N_kv, D, p.v_stride)) != AF_OK) return rc;
+  auto kern = fwd_tcgen05_kernel<T, D, ROPE>;
+  constexpr int smem = Cfg<D>::SMEM_BYTES;
+  AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int64_t ctas = (int64_t)args.num_m_blocks * p.B * p.H_q;
+  AF_REQUIRE(ctas <= 0x7fffffff, "too many tiles for one launch");
+  kern<<<(unsigned)ctas, ROPE ? 256 : 192, smem, st>>>(args, mq, mk, mv);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
+}
+
+template <typename T>
+int launch_dtype(const AfFwdParams& a, cudaStream_t st) {
+  const bool rope = a.p.rope != 0;
+  if (a.p.D == 64) return rope ? launch_impl<T, 64, true>(a, st) : launch_impl<T, 64, false>(a, st);
+  return rope ? launch_impl<T, 128, true>(a, st) : launch_impl<T, 128, false>(a, st);
+}
+
+}  // namespace
+
+bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_stride, const char** why) {
+  auto no = [&](const char* w) { if (why) *why = w; return false; };
+  if (p.dtype != AF_F16 && p.dtype != AF_BF16) return no("dtype is not f16/bf16");
+  if (p.D != 64 && p.D != 128) return no("head_dim is not 64 or 128");
+  if (p.norm_kind != AF_NORM_SOFTMAX) return no("normalisation is not softmax");
+  if (p.bias_kind == AF_BIAS_ADDITIVE) return no("additive bias");
+  if (p.N_q < 1 || p.N_kv < 1) return no("empty sequence");
+  if (p.mask_kind == AF_MASK_BLOCKS && (p.block_m % BM != 0 || p.block_n % BN != 0))
+    return no("block size is not a multiple of 128");
+  if (!tma_ok(p.q, p.B, p.H_q, p.N_q, p.q_stride) || !tma_ok(p.k, p.B, p.H_kv, p.N_kv, p.k_stride) ||
+      !tma_ok(p.v, p.B, p.H_kv, p.N_kv, p.v_stride))
+    return no("Q/K/V not TMA-addressable (16-byte aligned base and strides, unit inner stride)");
+  if (o_stride[3] != 1 || ((uintptr_t)o & 15) != 0 || o_stride[2] % 8 != 0 || o_stride[1] % 8 != 0 ||
+      o_stride[0] % 8 != 0)
+    return no("O rows not 16-byte aligned");
+  if (p.rope && (p.rope_stride_n % 8 != 0 || ((uintptr_t)p.cos & 15) != 0 || ((uintptr_t)p.sin & 15) != 0))
+    return no("cos/sin rows not 16-byte aligned");
+  return true;
+}
+
+int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
+  const char* why = nullptr;
+  if (!fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why))
+    return fail(AF_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+  if (a.p.dtype == AF_F16) return launch_dtype<__half>(a, st);
+  return launch_dtype<__nv_bfloat16>(a, st);
+}
+
+}  // namespace af

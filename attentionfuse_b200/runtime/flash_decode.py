@@ -1,0 +1,123 @@
+"""Split-K flash-decoding for query length 1.
+
+Mirrors the reference's decode path (attnfuse/runtime/flash_decode.py:46-187): the same
+eligibility rule (N_q == 1, N_kv >= 256, dense or ALiBi, no RoPE), fp32 workspaces allocated
+per call, a split launch followed by a combine launch.  Extensions: per-sequence valid
+lengths (``kv_lens``) and, for KV-sharded multi-GPU decoding, a key offset plus a packed
+(normalised O, LSE) partial output.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import functools
+from typing import Optional
+
+import torch
+
+from ..ir.high_level import Graph, BiasKind, MaskKind
+from . import _lib
+
+DECODE_HEAD_DIMS = (64, 128)
+DECODE_DTYPES = (torch.float16, torch.bfloat16)
+
+
+def can_use_flash_decode(graph: Graph, Q: torch.Tensor, K: torch.Tensor) -> bool:
+    if Q.shape[2] != 1 or K.shape[2] < 256:
+        return False
+    if {m.kind for m in graph.collect_masks()} - {MaskKind.FULL}:
+        return False
+    if {b.kind for b in graph.collect_biases()} - {BiasKind.ALIBI}:
+        return False
+    if graph.has_rope():
+        return False
+    # The mma.sync decode kernels are instantiated for these types and head dims; anything
+    # else takes the general forward kernel (N_q = 1 is a legal dense problem there).
+    if Q.dtype not in DECODE_DTYPES or Q.shape[3] not in DECODE_HEAD_DIMS:
+        return False
+    if K.stride(3) != 1 or Q.stride(3) != 1:
+        return False
+    if any(s % 8 for s in K.stride()[:3]) or K.data_ptr() % 16:
+        return False
+    return True
+
+
+@functools.lru_cache(maxsize=8)
+def _sm_count(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count
+
+
+def _pick_num_splits(B: int, H_kv: int, N_kv: int, device_index: int = 0) -> int:
+    """Split count (stands in for attnfuse/runtime/flash_decode.py:69-95)."""
+    return int(_lib.load().af_decode_num_splits(B, H_kv, N_kv, _sm_count(device_index)))
+
+
+def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device):
+    ws = torch.empty(num_splits * B * H_q * (D + 2), dtype=torch.float32, device=device)
+    n = num_splits * B * H_q
+    return ws[:n], ws[n:2 * n], ws[2 * n:]
+
+
+def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor,
+                     sm_scale: float, bias_kind: int, num_heads_kv: int,
+                     out: Optional[torch.Tensor], *, kv_lens: Optional[torch.Tensor] = None,
+                     alibi_slopes: Optional[torch.Tensor] = None, kv_offset: int = 0,
+                     q_positions: Optional[torch.Tensor] = None,
+                     partial: Optional[torch.Tensor] = None,
+                     num_splits: Optional[int] = None, workspace=None) -> torch.Tensor:
+    """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
+    when only the packed partial is requested)."""
+    lib = _lib.load()
+    B, H_q, _, D = Q.shape
+    _, H_kv, N_kv, _ = K.shape
+    if V.stride() != K.stride() and (V.stride(3) != 1 or any(s % 8 for s in V.stride()[:3])):
+        V = V.contiguous()
+    dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
+    if num_splits is None:
+        num_splits = _pick_num_splits(B, H_kv, N_kv, dev_index)
+    ws_m, ws_l, ws_acc = workspace if workspace is not None else decode_workspace(
+        num_splits, B, H_q, D, Q.device)
+
+    slopes = None
+    if bias_kind == 1:
+        if alibi_slopes is None:
+            from .dispatch import _alibi_slopes
+            alibi_slopes = _alibi_slopes(H_q, str(Q.device), str(Q.dtype))
+        slopes = alibi_slopes.to(device=Q.device, dtype=Q.dtype).contiguous()
+    if kv_lens is not None:
+        kv_lens = kv_lens.to(device=Q.device, dtype=torch.int32).contiguous()
+    if q_positions is not None:
+        q_positions = q_positions.to(device=Q.device, dtype=torch.int32).contiguous()
+
+    p = _lib.AfDecodeParams()
+    p.dtype = _lib.dtype_code(Q.dtype)
+    p.B, p.H_q, p.H_kv, p.N_kv, p.D = B, H_q, H_kv, N_kv, D
+    p.sm_scale, p.bias_kind, p.num_splits = float(sm_scale), int(bias_kind), int(num_splits)
+    p.q, p.q_stride = Q.data_ptr(), _lib.strides(Q)
+    p.k, p.k_stride = K.data_ptr(), _lib.strides(K)
+    p.v, p.v_stride = V.data_ptr(), _lib.strides(V)
+    p.slopes, p.kv_lens, p.q_positions = _lib.ptr(slopes), _lib.ptr(kv_lens), _lib.ptr(q_positions)
+    p.kv_offset = int(kv_offset)
+    p.ws_m, p.ws_l, p.ws_acc = ws_m.data_ptr(), ws_l.data_ptr(), ws_acc.data_ptr()
+    if out is not None:
+        p.o, p.o_stride = out.data_ptr(), _lib.strides(out)
+    if partial is not None:
+        p.partial = partial.data_ptr()
+    with torch.cuda.device(Q.device):
+        stream = _lib.current_stream(Q.device)
+        _lib.check(lib.af_decode_split(C.byref(p), stream), "af_decode_split")
+        _lib.check(lib.af_decode_combine(C.byref(p), stream), "af_decode_combine")
+    return out if out is not None else partial
+
+
+def combine_gathered(gathered: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Merge per-rank (normalised O, LSE) partials [G, B, H_q, D+1] that live in this GPU's
+    own memory into `out` (B, H_q, 1, D)."""
+    G, B, H_q, D1 = gathered.shape
+    assert gathered.dtype == torch.float32 and gathered.is_contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(out.device):
+        rc = lib.af_decode_combine_gathered(gathered.data_ptr(), G, B, H_q, D1 - 1,
+                                            _lib.dtype_code(out.dtype), out.data_ptr(),
+                                            _lib.strides(out), _lib.current_stream(out.device))
+    _lib.check(rc, "af_decode_combine_gathered")
+    return out

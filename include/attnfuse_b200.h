@@ -1,0 +1,162 @@
+/*
+ * attnfuse_b200.h -- C ABI of the sm_100a fused-attention library.
+ *
+ * The reference project has no native layer: its launch boundary is a set of Python
+ * functions that pass raw pointers, element strides and scalar flags to Triton kernels.
+ * Each entry point below replaces one of those launch sites; the comment above it names
+ * the reference function (path within the reference project : line) whose launch it
+ * stands in for.  All pointers are device pointers unless stated otherwise, all strides
+ * are in ELEMENTS (as in the reference's launches), every call is asynchronous on the
+ * given stream, and nothing here allocates or frees device memory unless stated.
+ *
+ * Return value: 0 on success; a negative AF_ERR_* code otherwise, with a human readable
+ * message available from af_last_error() (thread local).
+ */
+#ifndef ATTNFUSE_B200_H_
+#define ATTNFUSE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AF_ABI_VERSION 1
+
+typedef void* af_stream_t; /* a cudaStream_t */
+
+enum { AF_F16 = 0, AF_BF16 = 1, AF_F32 = 2 };
+/* MASK/BIAS/NORM codes are the reference's constexpr encodings
+ * (attnfuse/compiler/codegen.py:17-57), plus AF_MASK_BLOCKS for block lists. */
+enum { AF_MASK_FULL = 0, AF_MASK_CAUSAL = 1, AF_MASK_WINDOW = 2, AF_MASK_BLOCKS = 3 };
+enum { AF_BIAS_NONE = 0, AF_BIAS_ALIBI = 1, AF_BIAS_ADDITIVE = 2 };
+enum { AF_NORM_SOFTMAX = 0, AF_NORM_RELU = 1 };
+/* Kernel family: AUTO picks tcgen05 for f16/bf16 with D in {64,128} and softmax. */
+enum { AF_FAMILY_AUTO = 0, AF_FAMILY_FFMA = 1, AF_FAMILY_TCGEN05 = 2 };
+
+enum {
+  AF_OK = 0,
+  AF_ERR_INVALID = -1,     /* bad argument (shape, stride, alignment, enum)            */
+  AF_ERR_UNSUPPORTED = -2, /* composition has no kernel instantiation                  */
+  AF_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed                      */
+  AF_ERR_WORKSPACE = -4    /* caller-provided workspace too small                      */
+};
+
+/* Device status word values written by kernels whose bounded waits ran out. */
+enum { AF_STATUS_OK = 0, AF_STATUS_WAIT_TIMEOUT = 1 };
+
+/* One attention problem: shapes, composition flags and the read-only operands.
+ * Mirrors the argument list of the reference's forward launch
+ * (attnfuse/runtime/dispatch.py:196-214). */
+typedef struct AfProblem {
+  int32_t dtype;      /* AF_F16 / AF_BF16 / AF_F32: type of q,k,v,o,slopes,bias,cos,sin    */
+  int32_t family;     /* AF_FAMILY_*                                                       */
+  int32_t B, H_q, H_kv, N_q, N_kv, D;
+  float   sm_scale;
+  int32_t mask_kind;  /* AF_MASK_*                                                          */
+  int32_t window;     /* AF_MASK_WINDOW: keys with |i-j| < window are kept                  */
+  int32_t bias_kind;  /* AF_BIAS_*                                                          */
+  int32_t norm_kind;  /* AF_NORM_*                                                          */
+  int32_t rope;       /* 1: rotate Q and K (rotate-half) inside the kernel                  */
+  int32_t block_m, block_n; /* AF_MASK_BLOCKS: tile size the lists were built for          */
+  const void* q; int64_t q_stride[4];   /* (B, H_q,  N_q,  D)                               */
+  const void* k; int64_t k_stride[4];   /* (B, H_kv, N_kv, D)                               */
+  const void* v; int64_t v_stride[4];   /* (B, H_kv, N_kv, D)                               */
+  const void* slopes;                   /* [H_q], AF_BIAS_ALIBI                             */
+  const void* bias; int64_t bias_stride[4]; /* (B, H_q, N_q, N_kv), AF_BIAS_ADDITIVE       */
+  const void* cos; const void* sin; int64_t rope_stride_n; /* rows of D, inner stride 1    */
+  /* Block lists (int32).  Query-major: kv_num[h][qb], kv_idx[h][qb][slot];
+   * key-major (backward only): q_num[h][kb], q_idx[h][kb][slot].  A head stride of 0
+   * shares one mask between all heads (the reference's BlockMask has no head axis:
+   * attnfuse/runtime/block_mask.py:75-98). */
+  const int32_t* kv_num; const int32_t* kv_idx;
+  int64_t kv_num_stride_h, kv_idx_stride_h, kv_idx_stride_q;
+  const int32_t* q_num; const int32_t* q_idx;
+  int64_t q_num_stride_h, q_idx_stride_h, q_idx_stride_k;
+  int32_t* status;    /* optional device word, AF_STATUS_*; may be NULL                     */
+} AfProblem;
+
+typedef struct AfFwdParams {
+  AfProblem p;
+  void*   o;   int64_t o_stride[4];    /* (B, H_q, N_q, D), caller allocated               */
+  float*  lse; int64_t lse_stride[3];  /* (B, H_q, N_q) fp32 log-sum-exp, or NULL          */
+} AfFwdParams;
+
+typedef struct AfBwdParams {
+  AfProblem p;
+  const void*  o;   int64_t o_stride[4];
+  const void*  d_o; int64_t do_stride[4];
+  const float* lse; int64_t lse_stride[3];
+  float* delta;                       /* scratch (B, H_q, N_q) fp32 contiguous: rowsum(dO*O) */
+  void* dq; int64_t dq_stride[4];     /* like q                                            */
+  void* dk; int64_t dk_stride[4];     /* like k (summed over the query-head group)         */
+  void* dv; int64_t dv_stride[4];
+} AfBwdParams;
+
+/* Split-K decode (query length 1).  Workspaces are fp32:
+ *   ws_m, ws_l : [num_splits, B, H_q]      ws_acc : [num_splits, B, H_q, D]            */
+typedef struct AfDecodeParams {
+  int32_t dtype;
+  int32_t B, H_q, H_kv, N_kv, D;
+  float   sm_scale;
+  int32_t bias_kind;            /* AF_BIAS_NONE or AF_BIAS_ALIBI                           */
+  int32_t num_splits;
+  const void* q; int64_t q_stride[4];
+  const void* k; int64_t k_stride[4];
+  const void* v; int64_t v_stride[4];
+  const void* slopes;
+  const int32_t* kv_lens;       /* optional [B]: valid keys per batch row (<= N_kv); the
+                                   reference has a scalar N_KV only                       */
+  const int32_t* q_positions;   /* optional [B]: global query position used by ALiBi;
+                                   default kv_offset + (valid keys) - 1                    */
+  int32_t kv_offset;            /* global position of local key 0 (KV-sharded decode)      */
+  float* ws_m; float* ws_l; float* ws_acc;
+  void*  o; int64_t o_stride[4];  /* (B, H_q, 1, D) final output, or NULL                 */
+  float* partial;               /* optional [B, H_q, D+1] fp32: normalised O then LSE      */
+  int32_t* status;
+} AfDecodeParams;
+
+/* Replaces the forward launch in run_attention (attnfuse/runtime/dispatch.py:196-214)
+ * and, with mask_kind == AF_MASK_BLOCKS, the one in run_block_sparse
+ * (attnfuse/runtime/block_mask.py:246-270). */
+int af_fwd(const AfFwdParams* params, af_stream_t stream);
+
+/* Replaces the three launches of run_backward (attnfuse/runtime/backward.py:131-190:
+ * preproc, dK/dV, dQ) and of run_block_sparse_backward
+ * (attnfuse/runtime/block_mask.py:302-362).  dq/dk/dv are fully overwritten. */
+int af_bwd(const AfBwdParams* params, af_stream_t stream);
+
+/* Replaces the split launch of run_flash_decode (attnfuse/runtime/flash_decode.py:149-170). */
+int af_decode_split(const AfDecodeParams* params, af_stream_t stream);
+
+/* Replaces the combine launch of run_flash_decode (attnfuse/runtime/flash_decode.py:173-186).
+ * Writes o (if non-NULL) and partial (if non-NULL). */
+int af_decode_combine(const AfDecodeParams* params, af_stream_t stream);
+
+/* KV-sharded decode: merge G per-rank partials [G, B, H_q, D+1] (normalised O, LSE) that an
+ * all-gather placed in this GPU's own memory.  No counterpart in the reference, which is
+ * single-GPU. */
+int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int32_t H_q,
+                               int32_t D, int32_t dtype, void* o, const int64_t o_stride[4],
+                               af_stream_t stream);
+
+/* Split count for a decode problem: the reference's _pick_num_splits
+ * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  Host only. */
+int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count);
+
+/* Which family af_fwd / af_bwd would run for this problem (AF_FAMILY_*), or a negative
+ * error.  Host only; stands in for the reference's tile-table lookup
+ * (attnfuse/compiler/tiling.py:168-207). */
+int32_t af_query_family(const AfProblem* p, int32_t backward);
+
+/* Number of this library's kernel launches since load (all entry points). */
+int64_t af_launch_count(void);
+
+const char* af_last_error(void);
+int32_t     af_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATTNFUSE_B200_H_ */

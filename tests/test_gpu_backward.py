@@ -1,0 +1,104 @@
+"""Gradient parity: dQ, dK, dV from .backward() against torch.autograd through the oracle."""
+import pytest
+import torch
+
+import attentionfuse_b200 as af
+from attentionfuse_b200.runtime.dispatch import _alibi_slopes
+from oracle import attention_oracle as orc
+from tests._util import assert_close, golden, qkv
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@af.attention
+def dense(Q, K, V):
+    return af.softmax(af.scaled_dot_product(Q, K)) @ V
+
+
+@af.attention
+def causal(Q, K, V):
+    return af.softmax(af.causal(af.scaled_dot_product(Q, K))) @ V
+
+
+@af.attention
+def causal_rope(Q, K, V):
+    return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+
+def make_causal_alibi(h):
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.causal(af.alibi(af.scaled_dot_product(Q, K), h))) @ V
+    return fn
+
+
+def make_window(w):
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.sliding_window(af.scaled_dot_product(Q, K), w)) @ V
+    return fn
+
+
+def grads(fn, Q, K, V, dO, **kw):
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (Q, K, V))
+    out = fn(q, k, v, **kw)
+    out.backward(dO.to(DEV))
+    return out, q.grad, k.grad, v.grad
+
+
+def check(variant, shape, dtype):
+    B, Hq, Hkv, N, D = shape
+    Q, K, V = qkv(1100, B, Hq, Hkv, N, N, D, dtype)
+    dO = orc.randn(1103, (B, Hq, N, D), dtype)
+    kw, okw = {}, {"causal": variant.startswith("causal")}
+    fn = {"dense": dense, "causal": causal, "causal_rope": causal_rope, "causal_alibi": make_causal_alibi(Hq),
+          "window": make_window(23)}[variant]
+    if variant == "causal_rope":
+        cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
+        kw.update(cos=cos.to(DEV), sin=sin.to(DEV)); okw.update(cos=cos, sin=sin)
+    if variant == "causal_alibi":
+        okw["slopes"] = _alibi_slopes(Hq, "cpu", str(dtype))
+    if variant == "window":
+        okw["window"] = 23
+    out, dq, dk, dv = grads(fn, Q, K, V, dO, **kw)
+    O, dQ, dK, dV = orc.attention_grads(Q, K, V, dO, **okw)
+    assert dq.shape == Q.shape and dk.shape == K.shape and dv.shape == V.shape
+    assert_close(out, O, dtype, what=f"{variant} O")
+    assert_close(dq, dQ, dtype, grad=True, what=f"{variant} dQ")
+    assert_close(dk, dK, dtype, grad=True, what=f"{variant} dK")
+    assert_close(dv, dV, dtype, grad=True, what=f"{variant} dV")
+
+
+@pytest.mark.parametrize("variant", ["dense", "causal", "causal_rope", "causal_alibi", "window"])
+@pytest.mark.parametrize("shape", [(1, 4, 4, 64, 64), (2, 8, 2, 130, 64), (1, 4, 1, 200, 128), (1, 2, 2, 50, 32)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_backward(variant, shape, dtype):
+    check(variant, shape, dtype)
+
+
+def test_backward_golden():
+    g = golden("bwd_small_f32")
+    out, dq, dk, dv = grads(causal, g["Q"], g["K"], g["V"], g["dO"])
+    assert_close(out, g["O"], torch.float32, what="O")
+    assert_close(dq, g["dQ"], torch.float32, grad=True, what="dQ")
+    assert_close(dk, g["dK"], torch.float32, grad=True, what="dK")
+    assert_close(dv, g["dV"], torch.float32, grad=True, what="dV")
+    out, dq, dk, dv = grads(causal_rope, g["Q"], g["K"], g["V"], g["dO"], cos=g["cos"].to(DEV), sin=g["sin"].to(DEV))
+    assert_close(out, g["O_rope"], torch.float32, what="O rope")
+    assert_close(dq, g["dQ_rope"], torch.float32, grad=True, what="dQ rope")
+    assert_close(dk, g["dK_rope"], torch.float32, grad=True, what="dK rope")
+    assert_close(dv, g["dV_rope"], torch.float32, grad=True, what="dV rope")
+
+
+def test_no_grad_path_and_unsupported_falls_through():
+    Q, K, V = qkv(1200, 1, 2, 2, 64, 64, 64, torch.float16)
+
+    @af.attention
+    def relu(Q, K, V):
+        return af.relu_attention(af.scaled_dot_product(Q, K)) @ V
+
+    q = Q.to(DEV).requires_grad_(True)
+    out = relu(q, K.to(DEV), V.to(DEV))       # no backward for ReLU: inference path, no graph
+    assert not out.requires_grad

@@ -1,0 +1,122 @@
+"""Block-sparse forward / backward parity, shared and per-head masks, both kernel families."""
+import numpy as np
+import pytest
+import torch
+
+import attentionfuse_b200 as af
+from oracle import attention_oracle as orc
+from tests._util import assert_close, golden, qkv
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@af.attention
+def bs_attn(Q, K, V):
+    return af.softmax(af.block_sparse(af.scaled_dot_product(Q, K))) @ V
+
+
+def make_bs_alibi(h):
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.block_sparse(af.alibi(af.scaled_dot_product(Q, K), h))) @ V
+    return fn
+
+
+def bigbird_grid(nq, nk, seed):
+    """2 global key blocks, 2 global query block-rows, band of +-1, 3 random extra blocks per row."""
+    rng = np.random.default_rng(seed)
+    g = np.zeros((nq, nk), dtype=bool)
+    g[:, :2] = True
+    g[:2, :] = True
+    for i in range(nq):
+        g[i, max(0, i - 1):min(nk, i + 2)] = True
+        free = np.flatnonzero(~g[i])
+        if len(free):
+            g[i, rng.choice(free, size=min(3, len(free)), replace=False)] = True
+    return torch.from_numpy(g)
+
+
+@pytest.mark.parametrize("block", [64, 128])
+@pytest.mark.parametrize("pattern", ["all", "local", "bigbird", "strided"])
+def test_shared_mask_forward(block, pattern):
+    B, H, N, D = 2, 4, 512, 64
+    preds = {
+        "all": lambda q, k: torch.ones_like(q, dtype=torch.bool),
+        "local": lambda q, k: ((q // block) - (k // block)).abs() <= 1,
+        "bigbird": lambda q, k: ((q // block) == 0) | ((k // block) == 0) | (((q // block) - (k // block)).abs() <= 1),
+        "strided": lambda q, k: ((q // block) + (k // block)) % 2 == 0,
+    }
+    bm = af.create_block_mask(preds[pattern], N, N, block, block, device=DEV)
+    nb = N // block
+    expect = {"all": nb * nb, "local": 3 * nb - 2, "strided": (nb * nb) // 2 + nb % 2}.get(pattern)
+    if expect is not None:
+        assert bm.n_active == expect
+    Q, K, V = qkv(1300, B, H, H, N, N, D, torch.float16)
+    qi = torch.arange(N)[:, None].expand(N, N); kj = torch.arange(N)[None, :].expand(N, N)
+    want = orc.attention(Q, K, V, elem_mask=preds[pattern](qi, kj))
+    got = bs_attn(Q.to(DEV), K.to(DEV), V.to(DEV), block_mask=bm)
+    assert_close(got, want, torch.float16, what=f"{pattern} block={block}")
+
+
+def test_reference_builder_lists():
+    """create_block_mask reproduces the lists the reference builder emits (incl. round-up of partial tiles)."""
+    g = golden("block_sparse_small_f32")
+    preds = {
+        "bigbird": (lambda q, k: ((q // 64) == 0) | ((k // 64) == 0) | (((q // 64) - (k // 64)).abs() <= 1), 256),
+        "strided": (lambda q, k: ((q // 64) + (k // 64)) % 2 == 0, 256),
+        "ragged": (lambda q, k: (q - k).abs() <= 70, 200),
+    }
+    for name, (fn, n) in preds.items():
+        bm = af.create_block_mask(fn, n, n, 64, 64, device="cpu")
+        assert bm.n_active == int(g[f"{name}_n_active"])
+        assert torch.equal(bm.full_kv_num, g[f"{name}_full_kv_num"])
+        assert torch.equal(bm.q_num_blocks, g[f"{name}_q_num_blocks"])
+        w = g[f"{name}_full_kv_idx"].shape[1]
+        assert torch.equal(bm.full_kv_idx[:, :w], g[f"{name}_full_kv_idx"])
+        w = g[f"{name}_q_indices"].shape[1]
+        assert torch.equal(bm.q_indices[:, :w], g[f"{name}_q_indices"])
+    bm = af.create_block_mask(preds["bigbird"][0], 256, 256, 64, 64, device=DEV)
+    got = bs_attn(g["Q"].to(DEV), g["K"].to(DEV), g["V"].to(DEV), block_mask=bm)
+    assert_close(got, g["out_bigbird"], torch.float32, what="golden bigbird fp32")
+
+
+@pytest.mark.parametrize("block,dtype", [(128, torch.float16), (64, torch.bfloat16), (128, torch.float32)])
+def test_per_head_masks_forward_backward(block, dtype):
+    B, H, N, D = 1, 4, 1024, 64
+    nb = N // block
+    grids = torch.stack([bigbird_grid(nb, nb, 5000 + h) for h in range(H)])
+    bm = af.create_block_mask_per_head(grids, block, block, device=DEV)
+    assert bm.per_head and torch.equal(bm.dense_grid(), grids)
+    Q, K, V = qkv(1400, B, H, H, N, N, D, dtype)
+    dO = orc.randn(1403, (B, H, N, D), dtype)
+    want_parts = [orc.attention_grads(Q[:, h:h + 1], K[:, h:h + 1], V[:, h:h + 1], dO[:, h:h + 1],
+                                      elem_mask=orc.block_elem_mask(grids[h], block, block, N, N)) for h in range(H)]
+    O, dQ, dK, dV = (torch.cat([p[i] for p in want_parts], dim=1) for i in range(4))
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (Q, K, V))
+    out = bs_attn(q, k, v, block_mask=bm)
+    out.backward(dO.to(DEV))
+    assert_close(out, O, dtype, what="per-head O")
+    assert_close(q.grad, dQ, dtype, grad=True, what="per-head dQ")
+    assert_close(k.grad, dK, dtype, grad=True, what="per-head dK")
+    assert_close(v.grad, dV, dtype, grad=True, what="per-head dV")
+
+
+def test_empty_rows_alibi_gqa_and_errors():
+    B, Hq, Hkv, N, D, block = 1, 4, 2, 384, 64, 128
+    grid = torch.tensor([[1, 0, 0], [0, 0, 0], [1, 1, 1]], dtype=torch.bool)   # query block 1 sees nothing
+    bm = af.BlockMask.from_dense(grid, block, block, device=DEV)
+    Q, K, V = qkv(1500, B, Hq, Hkv, N, N, D, torch.bfloat16)
+    got = bs_attn(Q.to(DEV), K.to(DEV), V.to(DEV), block_mask=bm)
+    want = orc.attention(Q, K, V, elem_mask=orc.block_elem_mask(grid, block, block, N, N))
+    assert torch.all(got[:, :, 128:256] == 0) and torch.all(want[:, :, 128:256] == 0)
+    assert_close(got, want, torch.bfloat16, what="empty rows")
+    from attentionfuse_b200.runtime.dispatch import _alibi_slopes
+    got = make_bs_alibi(Hq)(Q.to(DEV), K.to(DEV), V.to(DEV), block_mask=bm)
+    want = orc.attention(Q, K, V, elem_mask=orc.block_elem_mask(grid, block, block, N, N),
+                         slopes=_alibi_slopes(Hq, "cpu", "torch.bfloat16"))
+    assert_close(got, want, torch.bfloat16, what="alibi + blocks + gqa")
+    with pytest.raises(RuntimeError, match="block_mask"):
+        bs_attn(Q.to(DEV), K.to(DEV), V.to(DEV))
+    with pytest.raises(TypeError):
+        bs_attn(Q.to(DEV), K.to(DEV), V.to(DEV), block_mask=grid)

@@ -1,0 +1,107 @@
+"""Decode (query length 1) parity: split-K kernel + combine against the oracle, with
+per-sequence lengths, ALiBi, GQA / MQA geometries and the KV-sharded merge."""
+import pytest
+import torch
+
+import attentionfuse_b200 as af
+from attentionfuse_b200.runtime.dispatch import _alibi_slopes
+from attentionfuse_b200.runtime.flash_decode import run_flash_decode, combine_gathered
+from attentionfuse_b200.runtime.sharded_decode import shard_bounds, sharded_decode
+from oracle import attention_oracle as orc
+from tests._util import assert_close, golden, qkv
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@af.attention
+def dense(Q, K, V):
+    return af.softmax(af.scaled_dot_product(Q, K)) @ V
+
+
+def make_alibi(h):
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.alibi(af.scaled_dot_product(Q, K), h)) @ V
+    return fn
+
+
+def lens_for(seed, B, L):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randint(L // 2, L + 1, (B,), generator=g, dtype=torch.int32)
+
+
+GEOM = [(32, 8), (64, 8), (64, 1), (8, 8), (12, 4)]
+
+
+@pytest.mark.parametrize("heads", GEOM, ids=lambda h: f"{h[0]}q{h[1]}kv")
+@pytest.mark.parametrize("L", [256, 1000, 4096])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_ragged(heads, L, dtype):
+    Hq, Hkv = heads
+    B, D = 3, 128
+    Q, K, V = qkv(900 + L, B, Hq, Hkv, 1, L, D, dtype)
+    lens = lens_for(L, B, L)
+    got = dense(Q.to(DEV), K.to(DEV), V.to(DEV), kv_lens=lens.to(DEV))
+    want = orc.attention(Q, K, V, kv_lens=lens)
+    assert_close(got, want, dtype, what=f"decode {heads} L={L}")
+    got_full = dense(Q.to(DEV), K.to(DEV), V.to(DEV))
+    assert_close(got_full, orc.attention(Q, K, V), dtype, what=f"decode full {heads} L={L}")
+
+
+def test_decode_d64_and_alibi():
+    B, Hq, Hkv, L, D = 2, 8, 2, 777, 64
+    Q, K, V = qkv(950, B, Hq, Hkv, 1, L, D, torch.float16)
+    lens = lens_for(5, B, L)
+    assert_close(dense(Q.to(DEV), K.to(DEV), V.to(DEV), kv_lens=lens.to(DEV)),
+                 orc.attention(Q, K, V, kv_lens=lens), torch.float16, what="d64")
+    slopes = _alibi_slopes(Hq, "cpu", "float16")
+    got = make_alibi(Hq)(Q.to(DEV), K.to(DEV), V.to(DEV))
+    assert_close(got, orc.attention(Q, K, V, slopes=slopes), torch.float16, what="alibi decode")
+    got = make_alibi(Hq)(Q.to(DEV), K.to(DEV), V.to(DEV), kv_lens=lens.to(DEV))
+    assert_close(got, orc.attention(Q, K, V, slopes=slopes, kv_lens=lens), torch.float16, what="alibi ragged")
+
+
+def test_decode_golden_and_fp32_route():
+    g = golden("decode_small_f32")
+    # fp32 takes the general forward kernel (the decode kernels are half precision)
+    got = dense(g["Q"].to(DEV), g["K"].to(DEV), g["V"].to(DEV))
+    assert_close(got, g["full"], torch.float32, what="fp32 decode via forward kernel")
+    Q, K, V = (g[k].to(torch.bfloat16) for k in ("Q", "K", "V"))
+    got = dense(Q.to(DEV), K.to(DEV), V.to(DEV), kv_lens=g["kv_lens"].to(DEV))
+    assert_close(got, orc.attention(Q, K, V, kv_lens=g["kv_lens"]), torch.bfloat16, what="golden ragged bf16")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 7, 16])
+def test_split_counts_agree(splits):
+    B, Hq, Hkv, L, D = 2, 32, 8, 2048, 128
+    Q, K, V = qkv(970, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+    lens = torch.tensor([1500, 64], dtype=torch.int32)
+    out = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    run_flash_decode(None, Q.to(DEV), K.to(DEV), V.to(DEV), 1.0 / D ** 0.5, 0, Hkv, out,
+                     kv_lens=lens.to(DEV), num_splits=splits)
+    assert_close(out, orc.attention(Q, K, V, kv_lens=lens), torch.bfloat16, what=f"splits={splits}")
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_kv_sharded_merge_emulated(world):
+    """The multi-GPU path on one GPU: every rank's local decode runs as its own pair of launches
+    (nothing waits on another rank), the partials are stacked as an all-gather would place them,
+    and the gathered-combine kernel merges them."""
+    B, Hq, Hkv, L, D = 4, 32, 8, 4096, 128
+    Q, K, V = qkv(990, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+    lens = torch.tensor([4096, 2048, 2049, 517], dtype=torch.int32)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    gathered = torch.empty(world, B, Hq, D + 1, dtype=torch.float32, device=DEV)
+    for r in range(world):
+        lo, hi = shard_bounds(L, world, r)
+
+        def fake_gather(buf, partial, r=r):
+            gathered[r].copy_(partial)
+        sharded_decode(q, k[:, :, lo:hi], v[:, :, lo:hi], lens.to(DEV), L, r, world,
+                       all_gather=fake_gather, combine=lambda buf, out: None)
+    out = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    combine_gathered(gathered, out)
+    assert_close(out, orc.attention(Q, K, V, kv_lens=lens), torch.bfloat16, what=f"sharded world={world}")
+    # rank with no valid keys for a row must report LSE = -inf there
+    assert torch.isinf(gathered[world - 1, 3, :, D]).all()
