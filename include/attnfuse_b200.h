@@ -24,6 +24,12 @@ extern "C" {
 
 #define AF_ABI_VERSION 1
 
+#if defined(__GNUC__)
+#define AF_API __attribute__((visibility("default")))
+#else
+#define AF_API
+#endif
+
 typedef void* af_stream_t; /* a cudaStream_t */
 
 enum { AF_F16 = 0, AF_BF16 = 1, AF_F32 = 2 };
@@ -120,41 +126,41 @@ typedef struct AfDecodeParams {
 /* Replaces the forward launch in run_attention (attnfuse/runtime/dispatch.py:196-214)
  * and, with mask_kind == AF_MASK_BLOCKS, the one in run_block_sparse
  * (attnfuse/runtime/block_mask.py:246-270). */
-int af_fwd(const AfFwdParams* params, af_stream_t stream);
+AF_API int af_fwd(const AfFwdParams* params, af_stream_t stream);
 
 /* Replaces the three launches of run_backward (attnfuse/runtime/backward.py:131-190:
  * preproc, dK/dV, dQ) and of run_block_sparse_backward
  * (attnfuse/runtime/block_mask.py:302-362).  dq/dk/dv are fully overwritten. */
-int af_bwd(const AfBwdParams* params, af_stream_t stream);
+AF_API int af_bwd(const AfBwdParams* params, af_stream_t stream);
 
 /* Replaces the split launch of run_flash_decode (attnfuse/runtime/flash_decode.py:149-170). */
-int af_decode_split(const AfDecodeParams* params, af_stream_t stream);
+AF_API int af_decode_split(const AfDecodeParams* params, af_stream_t stream);
 
 /* Replaces the combine launch of run_flash_decode (attnfuse/runtime/flash_decode.py:173-186).
  * Writes o (if non-NULL) and partial (if non-NULL). */
-int af_decode_combine(const AfDecodeParams* params, af_stream_t stream);
+AF_API int af_decode_combine(const AfDecodeParams* params, af_stream_t stream);
 
 /* KV-sharded decode: merge G per-rank partials [G, B, H_q, D+1] (normalised O, LSE) that an
  * all-gather placed in this GPU's own memory.  No counterpart in the reference, which is
  * single-GPU. */
-int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int32_t H_q,
+AF_API int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int32_t H_q,
                                int32_t D, int32_t dtype, void* o, const int64_t o_stride[4],
                                af_stream_t stream);
 
 /* Split count for a decode problem: the reference's _pick_num_splits
  * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  Host only. */
-int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count);
+AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count);
 
 /* Which family af_fwd / af_bwd would run for this problem (AF_FAMILY_*), or a negative
  * error.  Host only; stands in for the reference's tile-table lookup
  * (attnfuse/compiler/tiling.py:168-207). */
-int32_t af_query_family(const AfProblem* p, int32_t backward);
+AF_API int32_t af_query_family(const AfProblem* p, int32_t backward);
 
 /* Number of this library's kernel launches since load (all entry points). */
-int64_t af_launch_count(void);
+AF_API int64_t af_launch_count(void);
 
-const char* af_last_error(void);
-int32_t     af_abi_version(void);
+AF_API const char* af_last_error(void);
+AF_API int32_t     af_abi_version(void);
 
 #ifdef __cplusplus
 }
