@@ -1,0 +1,385 @@
+"""Benchmark of the fused-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  Headline workload: the Llama-3-8B attention layer shape, causal + RoPE,
+bf16 forward (Q [4,32,4096,128], K/V [4,8,4096,128], RoPE base 500000); a step is one forward
+pass over that batch.  `value` is whole-job TFLOP/s with inputs resident in HBM (algorithmic
+matmul FLOPs 4*B*H_q*D*N(N+1)/2 per step; under torchrun every rank runs its own batch, weak
+scaling, no collective).  `e2e` is the same metric through the public DSL call with pinned
+host buffers: host->device copies of Q/K/V and the device->host copy of O are inside the timed
+region.  `roofline` compares the forward kernel with the measured bf16 GEMM peak,
+`cpu_baseline` times the CPU oracle on a bounded sample of the same workload, and `extra`
+carries fwd+bwd TFLOP/s and decode GB/s (32k cache, per-sequence lengths) measured in the same
+run, including the KV-sharded decode when N > 1.
+
+`--impl reference` times the reference algorithm on the host cores only (the CPU oracle port:
+the reference project is pure Python/Triton and has no compiled CPU path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG4 = dict(B=4, H_q=32, H_kv=8, N=4096, D=128, rope_base=500000.0)
+DECODE = dict(B=16, H_q=32, H_kv=8, L=32768, D=128)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload,
+# from the ncu capture summarised under profiles/ (None until a capture exists).
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return json.loads(f.read_text()), "measured"
+    return FALLBACK_PEAKS, "fallback"
+
+
+def causal_pairs(n: int) -> int:
+    return n * (n + 1) // 2
+
+
+def fwd_flops(c) -> float:
+    return 4.0 * c["B"] * c["H_q"] * c["D"] * causal_pairs(c["N"])
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_cfg4(device, seed=4000):
+    from oracle import attention_oracle as orc
+    c = CFG4
+    dt = torch.bfloat16
+    Q = orc.randn(seed, (c["B"], c["H_q"], c["N"], c["D"]), dt)
+    K = orc.randn(seed + 1, (c["B"], c["H_kv"], c["N"], c["D"]), dt)
+    V = orc.randn(seed + 2, (c["B"], c["H_kv"], c["N"], c["D"]), dt)
+    dO = orc.randn(seed + 3, (c["B"], c["H_q"], c["N"], c["D"]), dt)
+    cos, sin = orc.build_rope_cache(c["N"], c["D"], c["rope_base"], dt)
+    return Q, K, V, dO, cos, sin
+
+
+def cpu_sample(Q, K, V, cos, sin, threads: int):
+    """Time the CPU oracle on one (batch, kv head) group of the workload: 4 query heads x 4096 x 4096."""
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(threads)
+    g = CFG4["H_q"] // CFG4["H_kv"]
+    q, k, v = Q[:1, :g].float(), K[:1, :1].float(), V[:1, :1].float()
+    c, s = cos.float(), sin.float()
+    orc.attention(q[:, :1, :512], k[:, :, :512], v[:, :, :512], causal=True, cos=c, sin=s)   # warm-up
+    best = float("inf")
+    for _ in range(2):
+        t0 = time.perf_counter()
+        orc.attention(q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16), causal=True, cos=cos, sin=sin)
+        best = min(best, time.perf_counter() - t0)
+    flops = 4.0 * g * CFG4["D"] * causal_pairs(CFG4["N"])
+    return flops / best / 1e12, best
+
+
+def run_reference(args):
+    """`--impl reference`: the reference algorithm (CPU oracle port) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    Q, K, V, dO, cos, sin = make_cfg4("cpu")
+    times = []
+    for i in range(args.warmup + args.steps):
+        tf, sec = cpu_sample(Q, K, V, cos, sin, threads)
+        if i >= args.warmup:
+            times.append(sec)
+        if sum(times) > 120:
+            break
+    g = CFG4["H_q"] // CFG4["H_kv"]
+    flops = 4.0 * g * CFG4["D"] * causal_pairs(CFG4["N"])
+    ms = 1e3 * sum(times) / len(times)
+    value = flops / (ms * 1e-3) / 1e12
+    sample = f"1 of {CFG4['B'] * CFG4['H_kv']} (batch, kv-head) groups per step: {g} query heads x 4096 x 4096, fp32 eager"
+    print(json.dumps({
+        "impl": "reference", "metric": "causal_rope_fwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama3-8b attention layer, causal+RoPE forward, Q[4,32,4096,128] K/V[4,8,4096,128]",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def time_region(fn, steps: int, dist_on: bool):
+    """Device time of `steps` calls, bracketed by barrier + synchronize; max over ranks (ms)."""
+    import torch.distributed as dist
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+    ms = torch.tensor([start.elapsed_time(end)], device="cuda")
+    if dist_on:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip fwd+bwd / decode side measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    import attentionfuse_b200 as af
+    from attentionfuse_b200.runtime import _lib
+    from attentionfuse_b200.runtime.dispatch import run_attention
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode, decode_workspace, _pick_num_splits
+    from attentionfuse_b200.runtime.sharded_decode import shard_bounds, sharded_decode
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_on = world > 1
+    if dist_on:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    pk, pk_kind = peaks()
+
+    @af.attention
+    def causal_rope(Q, K, V):
+        return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+    Qh, Kh, Vh, dOh, cosh, sinh = make_cfg4("cpu", seed=4000 + 10 * rank)
+    Qp, Kp, Vp = Qh.pin_memory(), Kh.pin_memory(), Vh.pin_memory()
+    Q, K, V, dO = Qh.to(dev), Kh.to(dev), Vh.to(dev), dOh.to(dev)
+    cos, sin = cosh.to(dev), sinh.to(dev)
+    out = torch.empty_like(Q)
+    graph = causal_rope(Q, K, V, return_graph=True)
+    flops = fwd_flops(CFG4)
+
+    def step():
+        run_attention(graph, Q, K, V, cos=cos, sin=sin, out=out)
+
+    for _ in range(args.warmup):
+        step()
+    launches0 = _lib.launch_count()
+    with ClockSampler(local_rank) as clk:
+        ms_total = time_region(step, args.steps, dist_on)
+    launches = _lib.launch_count() - launches0
+    ms_step = ms_total / args.steps
+    value = world * flops / (ms_step * 1e-3) / 1e12
+    per_gpu = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers in, O back to the host, through the DSL call
+    Qd, Kd, Vd = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+    Oh = torch.empty(Q.shape, dtype=Q.dtype).pin_memory()
+
+    def e2e_step():
+        Qd.copy_(Qp, non_blocking=True); Kd.copy_(Kp, non_blocking=True); Vd.copy_(Vp, non_blocking=True)
+        o = causal_rope(Qd, Kd, Vd, cos=cos, sin=sin)
+        Oh.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = time_region(e2e_step, e2e_steps, dist_on) / e2e_steps
+    h2d = Qp.numel() * 2 + Kp.numel() * 2 + Vp.numel() * 2
+    d2h = Oh.numel() * 2
+
+    result = {
+        "metric": "causal_rope_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "llama3-8b attention layer, causal+RoPE forward, Q[4,32,4096,128] K/V[4,8,4096,128], "
+                               "RoPE base 5e5; every rank runs its own batch",
+                   "l2": "working set 335 MB per step exceeds the 126 MB L2", "partition": f"batch x kv-head, {world} rank(s), no collective"},
+        "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": launches,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": per_gpu / pk["bf16_tflops"], "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
+                     "peak_kind": f"{pk_kind} cuBLAS bf16 burst", "kernel": "fwd_tcgen05_kernel<bf16,128,rope>",
+                     "frac_of_nominal_2250": per_gpu / 2250.0},
+    }
+
+    extra = {}
+    if not args.no_extra:
+        try:
+            # ---- fwd + bwd (training step of the layer): 14*B*H_q*D*P algorithmic FLOPs
+            def train_step():
+                q = Q.detach().requires_grad_(True); k = K.detach().requires_grad_(True); v = V.detach().requires_grad_(True)
+                o = causal_rope(q, k, v, cos=cos, sin=sin)
+                o.backward(dO)
+            train_step()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter(); train_step(); torch.cuda.synchronize()
+            one = time.perf_counter() - t0
+            n = 1 if one > 2.0 else max(2, min(10, int(4.0 / max(one, 1e-3))))
+            tb = time_region(train_step, n, dist_on) / n
+            fb = 3.5 * flops / (tb * 1e-3) / 1e12
+            extra["fwd_bwd"] = {"tflops_per_gpu": fb, "ms_per_step": tb, "frac_of_measured_peak": fb / pk["bf16_tflops"],
+                                "frac_of_nominal_2250": fb / 2250.0}
+        except Exception as e:  # keep the headline line alive
+            extra["fwd_bwd"] = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            extra["decode"] = bench_decode(dev, rank, world, dist_on, pk)
+        except Exception as e:
+            extra["decode"] = {"error": f"{type(e).__name__}: {e}"}
+    result["extra"] = extra
+
+    if rank == 0:
+        try:
+            threads = os.cpu_count() or 1
+            tf, sec = cpu_sample(Qh, Kh, Vh, cosh, sinh, threads)
+            result["cpu_baseline"] = {
+                "value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"1 of 32 (batch, kv-head) groups: 4 query heads x 4096 x 4096 causal+RoPE, fp32 eager, {sec:.2f} s"}
+        except Exception as e:
+            result["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                                      "sample": f"failed: {e}"}
+        print(json.dumps(result))
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def bench_decode(dev, rank, world, dist_on, pk):
+    """GQA decode at a 32k cache with per-sequence lengths in [L/2, L]: achieved HBM GB/s.
+    With more than one rank also the KV-sharded step (local split-K, all-gather, merge)."""
+    import torch.distributed as dist
+    from oracle import attention_oracle as orc
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode, decode_workspace, _pick_num_splits
+    from attentionfuse_b200.runtime.sharded_decode import shard_bounds, sharded_decode
+    c = DECODE
+    B, Hq, Hkv, L, D = c["B"], c["H_q"], c["H_kv"], c["L"], c["D"]
+    dt = torch.bfloat16
+    g = torch.Generator(device="cpu").manual_seed(3000)
+    lens = torch.randint(L // 2, L + 1, (B,), generator=g, dtype=torch.int32)
+    gen = torch.Generator(device=dev).manual_seed(3001)
+    n_buf = 3   # rotate caches so that no K/V byte of a step is still in L2 from the previous one
+    caches = [(torch.randn(B, Hkv, L, D, generator=gen, device=dev, dtype=dt),
+               torch.randn(B, Hkv, L, D, generator=gen, device=dev, dtype=dt)) for _ in range(n_buf)]
+    Q = torch.randn(B, Hq, 1, D, generator=gen, device=dev, dtype=dt)
+    out = torch.empty_like(Q)
+    lens_d = lens.to(dev)
+    S = _pick_num_splits(B, Hkv, L, dev.index or 0)
+    ws = decode_workspace(S, B, Hq, D, dev)
+    sm_scale = 1.0 / D ** 0.5
+    bytes_step = 2.0 * Hkv * D * 2 * float(lens.sum()) + 2.0 * B * Hq * D * 2
+    it = [0]
+
+    def step():
+        Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
+        run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, num_splits=S, workspace=ws)
+
+    for _ in range(5):
+        step()
+    ms = time_region(step, 30, dist_on) / 30
+    gbs = bytes_step / (ms * 1e-3) / 1e9
+    res = {"gbs_per_gpu": gbs, "ms_per_step": ms, "bytes_per_step": bytes_step, "num_splits": S,
+           "frac_of_measured_hbm": gbs / pk["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
+           "config": "B16 H32/8 D128 L32768 bf16, lengths U[L/2, L], 3 rotating caches (2.1 GB each)"}
+    # CUDA-graph replay of the two launches (launch overhead matters at this step time)
+    try:
+        gr = torch.cuda.CUDAGraph()
+        Kc, Vc = caches[0]
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, num_splits=S, workspace=ws)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gr, stream=s):
+                for i in range(n_buf):
+                    run_flash_decode(None, Q, caches[i][0], caches[i][1], sm_scale, 0, Hkv, out, kv_lens=lens_d,
+                                     num_splits=S, workspace=ws)
+        torch.cuda.synchronize()
+        msg = time_region(gr.replay, 10, dist_on) / (10 * n_buf)
+        res["graph_gbs_per_gpu"] = bytes_step / (msg * 1e-3) / 1e9
+        res["graph_ms_per_step"] = msg
+    except Exception as e:
+        res["graph_error"] = f"{type(e).__name__}: {e}"
+
+    if dist_on:
+        lo, hi = shard_bounds(L, world, rank)
+        Kl = caches[0][0][:, :, : hi - lo].contiguous(); Vl = caches[0][1][:, :, : hi - lo].contiguous()
+        gather = torch.empty(world, B, Hq, D + 1, dtype=torch.float32, device=dev)
+
+        def sharded():
+            sharded_decode(Q, Kl, Vl, lens_d, L, rank, world, out=out, gather_buffer=gather)
+        for _ in range(5):
+            sharded()
+        mss = time_region(sharded, 30, True) / 30
+        res["kv_sharded"] = {"world": world, "ms_per_step": mss, "speedup_vs_1gpu_step": ms / mss,
+                             "aggregate_gbs": bytes_step / (mss * 1e-3) / 1e9}
+    return res
+
+
+if __name__ == "__main__":
+    main()
