@@ -75,6 +75,13 @@ int af_fwd(const AfFwdParams* params, af_stream_t stream) {
   return launch_fwd_ffma(a, st);
 }
 
+int64_t af_fwd_workspace_bytes(const AfFwdParams* params) {
+  if (params == nullptr) return 0;
+  const AfFwdParams& a = *params;
+  if (a.p.family == AF_FAMILY_FFMA || !fwd_tcgen05_supports(a.p, a.o, a.o_stride, nullptr)) return 0;
+  return fwd_tcgen05_workspace_bytes(a.p);
+}
+
 int af_bwd(const AfBwdParams* params, af_stream_t stream) {
   if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
   const AfBwdParams& a = *params;

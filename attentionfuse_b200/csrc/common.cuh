@@ -65,6 +65,7 @@ int check_cuda(cudaError_t e, const char* what);
 // ---------------------------------------------------------------------------------------
 int launch_fwd_ffma(const AfFwdParams& a, cudaStream_t st);
 int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st);
+int64_t fwd_tcgen05_workspace_bytes(const AfProblem& p);
 bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_stride,
                           const char** why);
 

@@ -24,15 +24,19 @@
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status word, drains and
 // frees its TMEM.
+#pragma once
 #include <cuda.h>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace af {
-namespace {
+namespace tc {
 
 using namespace ptx;
+
+enum { ROPE_NONE = 0, ROPE_FUSED = 1 };   // a pre-pass rotation runs the ROPE_NONE kernels
+enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };  // element-level mask of the instantiation
 
 constexpr int BM = 128;
 constexpr int BN = 128;
@@ -165,12 +169,23 @@ __device__ __forceinline__ void rope_row(uint32_t tile, int r, const T* cos_row,
   }
 }
 
-template <typename T, int D, bool ROPE>
-__global__ void __launch_bounds__(ROPE ? 256 : 192, 1)
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One instantiation per composition: element type, head_dim, RoPE mode, element-level mask and
+// ALiBi are compile-time, so the per-element code of the softmax group carries no run-time
+// branches on the composition.
+template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
+__global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 256 : 192, 1)
 fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
   using C = Cfg<D>;
   constexpr int STAGES = C::STAGES;
+  constexpr bool ROT_K = (ROPE == ROPE_FUSED);
   constexpr int AB_FMT = (Elem<T>::code == AF_BF16) ? 1 : 0;
   constexpr uint32_t IDESC_QK = umma_idesc_f16(AB_FMT, BM, BN, 0, 0);
   constexpr uint32_t IDESC_PV = umma_idesc_f16(AB_FMT, BM, D, 0, 1);
@@ -191,8 +206,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 
   // Tile assignment: the heaviest query tiles (causal: the last ones) are issued first.
   const int bh_count = p.B * p.H_q;
-  const int m_blk = (p.mask_kind == AF_MASK_CAUSAL) ? (args.num_m_blocks - 1 - (int)(blockIdx.x / bh_count))
-                                                    : (int)(blockIdx.x / bh_count);
+  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - (int)(blockIdx.x / bh_count))
+                                            : (int)(blockIdx.x / bh_count);
   const int bh = blockIdx.x % bh_count;
   const int b = bh / p.H_q, h = bh % p.H_q;
   const int h_kv = h / (p.H_q / p.H_kv);
@@ -258,11 +273,11 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   } else if (warp == 5) {
     // ============================== MMA issuer ==============================
     if (lane == 0 && n_tiles > 0) {
-      bool ok = mbar_wait(ROPE ? &bars->q_ready : &bars->q_full, 0, abort_flag);
+      bool ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, 0, abort_flag);
       tc_fence_after_sync();
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES, t = j & 1;
-        if (!mbar_wait(ROPE ? &bars->k_ready[s] : &bars->k_full[s], (j / STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(ROT_K ? &bars->k_ready[s] : &bars->k_full[s], (j / STAGES) & 1, abort_flag)) return false;
         if (j >= 2 && !mbar_wait(&bars->pv_done[t], ((j >> 1) - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
@@ -302,7 +317,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     // ============================== softmax / epilogue ==============================
     const int row = m0 + tid;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    if (ROPE && n_tiles > 0) {
+    if (ROPE != ROPE_NONE && n_tiles > 0) {
       if (mbar_wait(&bars->q_full, 0, abort_flag)) {
         if (row < p.N_q)
           rope_row<T, D>(sQ, tid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
@@ -311,9 +326,9 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         mbar_arrive(&bars->q_ready);
       }
     }
-    const float scale2 = p.sm_scale * kLog2e;
-    const float slope2 = (p.bias_kind == AF_BIAS_ALIBI) ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
-    float m_ref = -INFINITY, l_sum = 0.f;
+    const float scale2 = p.sm_scale * kLog2e;     // > 0 (checked on the host)
+    const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
+    float m_ref = -INFINITY, l_sum = 0.f;         // m_ref in log2 units of the scaled score
     bool alive = true;
 
     for (int j = 0; j < n_tiles; ++j) {
@@ -322,36 +337,46 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       if (!mbar_wait(&bars->s_full[t], (j >> 1) & 1, abort_flag)) { alive = false; break; }
       tc_fence_after_sync();
       const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
-      uint32_t xr[BN];   // fp32 bit patterns of this row's scores
+      uint32_t xr[BN];   // fp32 bit patterns of this row's raw scores
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, &xr[c * 32]);
       tmem_wait_ld();
 
+      // Tile-level decision: only edge / diagonal tiles pay for element masking.
       bool need_mask = key0 + BN > p.N_kv;
-      if (p.mask_kind == AF_MASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
-      if (p.mask_kind == AF_MASK_WINDOW)
+      if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
+      if (EMASK == EMASK_WINDOW)
         need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
-
-      float mx = -INFINITY;
+      const int rel = row - key0;                 // key index c is kept iff ...
+      if (need_mask) {
+        const int kmax = p.N_kv - key0;           // ... c < kmax
 #pragma unroll
-      for (int c = 0; c < BN; ++c) {
-        float v = __uint_as_float(xr[c]) * scale2;
-        if (p.bias_kind == AF_BIAS_ALIBI) v -= slope2 * (float)abs(row - (key0 + c));
-        if (need_mask) {
-          const int key = key0 + c;
-          bool keep = key < p.N_kv;
-          if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (row >= key);
-          if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(row - key) < p.window);
-          v = keep ? v : -INFINITY;
+        for (int c = 0; c < BN; ++c) {
+          bool keep = c < kmax;
+          if (EMASK == EMASK_CAUSAL) keep = keep && (c <= rel);
+          if (EMASK == EMASK_WINDOW) keep = keep && (c - rel < p.window) && (rel - c < p.window);
+          xr[c] = keep ? xr[c] : 0xff800000u;     // -inf
         }
-        xr[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
       }
+      if (ALIBI) {
+        const float relf = (float)rel;
+#pragma unroll
+        for (int c = 0; c < BN; ++c)
+          xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < BN; c += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
       const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
       const float m_next = bump ? mx : m_ref;
-      const float alpha = bump ? exp2f(m_ref - m_next) : 1.f;
+      const float alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
       m_ref = m_next;
-      const float m_use = (m_next == -INFINITY) ? 0.f : m_next;
+      const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
 
       if (j > 0 && __any_sync(0xffffffffu, bump)) {
         // The accumulator is expressed relative to the old reference: rescale it in TMEM once
@@ -370,15 +395,21 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         tmem_wait_st();
       }
 
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[BN / 2];
 #pragma unroll
-      for (int c = 0; c < BN; c += 2) {
-        const float p0 = exp2f(__uint_as_float(xr[c]) - m_use), p1 = exp2f(__uint_as_float(xr[c + 1]) - m_use);
-        rs += p0 + p1;
-        pk[c >> 1] = Pack2<T>::run(p0, p1);
+      for (int c = 0; c < BN; c += 4) {
+        float e[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float x = __uint_as_float(xr[c + u]);
+          e[u] = ex2_approx(ALIBI ? x + neg_m : fmaf(x, scale2, neg_m));
+          rs4[u] += e[u];
+        }
+        pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
+        pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
       }
-      l_sum = l_sum * alpha + rs;
+      l_sum = l_sum * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       tmem_st32(s_tmem, &pk[0]);
       tmem_st32(s_tmem + 32, &pk[32]);
       tmem_wait_st();
@@ -423,7 +454,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
             m_ref * kLn2 + logf(safe_l);
     }
-  } else if (ROPE && warp >= 6) {
+  } else if (ROT_K && warp >= 6) {
     // ============================== K rotation group ==============================
     // Two warps (eight warps per CTA keep 255 registers per thread available to the softmax
     // group); each thread rotates two key rows of the tile.
@@ -456,111 +487,55 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 }
 
 // ---------------------------------------------------------------------------------------
-// Host side
+// Launch of one instantiation (tensor maps are encoded by the host file)
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(sym);
-  }();
-  return fn;
-}
-
-// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x 128 x 1 x 1.
-int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t esz = 2;
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
-  // Strides of extent-1 dimensions are never used for addressing; give them a legal value.
-  cuuint64_t sN = (cuuint64_t)st[2] * esz, sH = (cuuint64_t)st[1] * esz, sB = (cuuint64_t)st[0] * esz;
-  if (N == 1) sN = (cuuint64_t)D * esz;
-  if (H == 1) sH = sN * (cuuint64_t)N;
-  if (B == 1) sB = sH * (cuuint64_t)H;
-  cuuint64_t strides[3] = {sN, sH, sB};
-  cuuint32_t box[4] = {64, 128, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(out, dtype == AF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return AF_OK;
-}
-
-bool tma_ok(const void* ptr, int B, int H, int N, const int64_t* st) {
-  if (((uintptr_t)ptr & 15) != 0 || st[3] != 1) return false;
-  if (N > 1 && (st[2] <= 0 || st[2] % 8 != 0)) return false;
-  if (H > 1 && (st[1] <= 0 || st[1] % 8 != 0)) return false;
-  if (B > 1 && (st[0] <= 0 || st[0] % 8 != 0)) return false;
-  return true;
-}
-
-template <typename T, int D, bool ROPE>
-int launch_impl(const AfFwdParams& a, cudaStream_t st) {
-  const AfProblem& p = a.p;
-  TcArgs args;
-  args.a = a;
-  args.num_m_blocks = (p.N_q + BM - 1) / BM;
-  args.kv_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_n / BN : 1;
-  args.q_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_m / BM : 1;
-  CUtensorMap mq, mk, mv;
-  int rc;
-  if ((rc = make_map(&mq, p.dtype, p.q, p.B, p.H_q, p.N_q, D, p.q_stride)) != AF_OK) return rc;
-  if ((rc = make_map(&mk, p.dtype, p.k, p.B, p.H_kv, p.N_kv, D, p.k_stride)) != AF_OK) return rc;
-  if ((rc = make_map(&mv, p.dtype, p.v, p.B, p.H_kv, p.N_kv, D, p.v_stride)) != AF_OK) return rc;
-  auto kern = fwd_tcgen05_kernel<T, D, ROPE>;
+template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
+int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                    cudaStream_t st) {
+  auto kern = fwd_tcgen05_kernel<T, D, ROPE, EMASK, ALIBI>;
   constexpr int smem = Cfg<D>::SMEM_BYTES;
-  AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  static bool configured = false;   // benign race: the attribute call is idempotent
+  if (!configured) {
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const AfProblem& p = args.a.p;
   const int64_t ctas = (int64_t)args.num_m_blocks * p.B * p.H_q;
-  AF_REQUIRE(ctas <= 0x7fffffff, "too many tiles for one launch");
-  kern<<<(unsigned)ctas, ROPE ? 256 : 192, smem, st>>>(args, mq, mk, mv);
+  kern<<<(unsigned)ctas, ROPE == ROPE_FUSED ? 256 : 192, smem, st>>>(args, mq, mk, mv);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
 }
 
-template <typename T>
-int launch_dtype(const AfFwdParams& a, cudaStream_t st) {
-  const bool rope = a.p.rope != 0;
-  if (a.p.D == 64) return rope ? launch_impl<T, 64, true>(a, st) : launch_impl<T, 64, false>(a, st);
-  return rope ? launch_impl<T, 128, true>(a, st) : launch_impl<T, 128, false>(a, st);
+// Composition -> instantiation table for one (dtype, head_dim, RoPE mode); defined in the
+// per-(D, RoPE) translation units so that they compile in parallel.
+template <typename T, int D, int ROPE>
+int launch_composition(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                       cudaStream_t st) {
+  const AfProblem& p = args.a.p;
+  const int em = p.mask_kind == AF_MASK_CAUSAL ? EMASK_CAUSAL : p.mask_kind == AF_MASK_WINDOW ? EMASK_WINDOW : EMASK_NONE;
+  const bool alibi = p.bias_kind == AF_BIAS_ALIBI;
+  switch (em * 2 + (alibi ? 1 : 0)) {
+    case 0: return launch_instance<T, D, ROPE, EMASK_NONE, false>(args, mq, mk, mv, st);
+    case 1: return launch_instance<T, D, ROPE, EMASK_NONE, true>(args, mq, mk, mv, st);
+    case 2: return launch_instance<T, D, ROPE, EMASK_CAUSAL, false>(args, mq, mk, mv, st);
+    case 3: return launch_instance<T, D, ROPE, EMASK_CAUSAL, true>(args, mq, mk, mv, st);
+    case 4: return launch_instance<T, D, ROPE, EMASK_WINDOW, false>(args, mq, mk, mv, st);
+    default: return launch_instance<T, D, ROPE, EMASK_WINDOW, true>(args, mq, mk, mv, st);
+  }
 }
 
-}  // namespace
+// Entry points of the instantiation units: dtype is AF_F16 / AF_BF16.
+int launch_d64_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d64_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d128_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d128_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 
-bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_stride, const char** why) {
-  auto no = [&](const char* w) { if (why) *why = w; return false; };
-  if (p.dtype != AF_F16 && p.dtype != AF_BF16) return no("dtype is not f16/bf16");
-  if (p.D != 64 && p.D != 128) return no("head_dim is not 64 or 128");
-  if (p.norm_kind != AF_NORM_SOFTMAX) return no("normalisation is not softmax");
-  if (p.bias_kind == AF_BIAS_ADDITIVE) return no("additive bias");
-  if (p.N_q < 1 || p.N_kv < 1) return no("empty sequence");
-  if (p.mask_kind == AF_MASK_BLOCKS && (p.block_m % BM != 0 || p.block_n % BN != 0))
-    return no("block size is not a multiple of 128");
-  if (!tma_ok(p.q, p.B, p.H_q, p.N_q, p.q_stride) || !tma_ok(p.k, p.B, p.H_kv, p.N_kv, p.k_stride) ||
-      !tma_ok(p.v, p.B, p.H_kv, p.N_kv, p.v_stride))
-    return no("Q/K/V not TMA-addressable (16-byte aligned base and strides, unit inner stride)");
-  if (o_stride[3] != 1 || ((uintptr_t)o & 15) != 0 || o_stride[2] % 8 != 0 || o_stride[1] % 8 != 0 ||
-      o_stride[0] % 8 != 0)
-    return no("O rows not 16-byte aligned");
-  if (p.rope && (p.rope_stride_n % 8 != 0 || ((uintptr_t)p.cos & 15) != 0 || ((uintptr_t)p.sin & 15) != 0))
-    return no("cos/sin rows not 16-byte aligned");
-  return true;
-}
+#define AF_DEFINE_TC_UNIT(NAME, DIM, ROPE_MODE)                                                              \
+  int NAME(int dtype, const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, \
+           cudaStream_t st) {                                                                                \
+    if (dtype == AF_F16) return launch_composition<__half, DIM, ROPE_MODE>(args, mq, mk, mv, st);            \
+    return launch_composition<__nv_bfloat16, DIM, ROPE_MODE>(args, mq, mk, mv, st);                          \
+  }
 
-int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
-  const char* why = nullptr;
-  if (!fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why))
-    return fail(AF_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
-  if (a.p.dtype == AF_F16) return launch_dtype<__half>(a, st);
-  return launch_dtype<__nv_bfloat16>(a, st);
-}
-
+}  // namespace tc
 }  // namespace af

@@ -1,0 +1,199 @@
+// Host side of the tcgen05 forward: support predicate, TMA descriptor encoding, RoPE mode
+// selection (fused in shared memory vs. a one-off K pre-rotation into caller workspace) and
+// dispatch to the per-(head_dim, RoPE mode) instantiation units.
+#include "fwd_tcgen05.cuh"
+
+namespace af {
+namespace {
+
+using namespace tc;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x 128 x 1 x 1.
+int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t esz = 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  // Strides of extent-1 dimensions are never used for addressing; give them a legal value.
+  cuuint64_t sN = (cuuint64_t)st[2] * esz, sH = (cuuint64_t)st[1] * esz, sB = (cuuint64_t)st[0] * esz;
+  if (N == 1) sN = (cuuint64_t)D * esz;
+  if (H == 1) sH = sN * (cuuint64_t)N;
+  if (B == 1) sB = sH * (cuuint64_t)H;
+  cuuint64_t strides[3] = {sN, sH, sB};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, dtype == AF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return AF_OK;
+}
+
+bool tma_ok(const void* ptr, int B, int H, int N, const int64_t* st) {
+  if (((uintptr_t)ptr & 15) != 0 || st[3] != 1) return false;
+  if (N > 1 && (st[2] <= 0 || st[2] % 8 != 0)) return false;
+  if (H > 1 && (st[1] <= 0 || st[1] % 8 != 0)) return false;
+  if (B > 1 && (st[0] <= 0 || st[0] % 8 != 0)) return false;
+  return true;
+}
+
+// RoPE pre-pass: dst[b, h, n, :] = rope(src[b, h, n, :]) as contiguous (B, H, N, D) for Q and K
+// in one launch; fp32 math, one rounding to T -- the same arithmetic as the in-kernel rotation.
+// One thread per pair of 16-byte chunks (d, d + D/2).
+struct RotateJob {
+  const void* src; void* dst;
+  int64_t s0, s1, s2;
+  int H, N;
+  int64_t chunks;   // B * H * N * (D / 16)
+};
+
+template <typename T, int D>
+__global__ void rope_prepass_kernel(const RotateJob jq, const RotateJob jk, const T* __restrict__ cos_,
+                                    const T* __restrict__ sin_, int64_t sr) {
+  constexpr int HC = D / 16;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool is_q = idx < jq.chunks;
+  const RotateJob& job = is_q ? jq : jk;
+  if (!is_q) idx -= jq.chunks;
+  if (idx >= job.chunks) return;
+  const int c = (int)(idx % HC);
+  const int64_t row = idx / HC;
+  const int n = (int)(row % job.N);
+  const int h = (int)((row / job.N) % job.H);
+  const int64_t b = row / ((int64_t)job.N * job.H);
+  const T* src = reinterpret_cast<const T*>(job.src) + b * job.s0 + (int64_t)h * job.s1 + (int64_t)n * job.s2;
+  T* dst = reinterpret_cast<T*>(job.dst) + row * D;
+  const uint4 xl = *reinterpret_cast<const uint4*>(src + c * 8), xh = *reinterpret_cast<const uint4*>(src + D / 2 + c * 8);
+  const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + c * 8));
+  const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + D / 2 + c * 8));
+  const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + c * 8));
+  const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + D / 2 + c * 8));
+  const uint32_t xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
+  const uint32_t clw[4] = {cl.x, cl.y, cl.z, cl.w}, chw[4] = {ch.x, ch.y, ch.z, ch.w};
+  const uint32_t slw[4] = {sl.x, sl.y, sl.z, sl.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+  uint32_t ol[4], oh[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x1 = Pack2<T>::unpack(xlw[i]), x2 = Pack2<T>::unpack(xhw[i]);
+    const float2 c1 = Pack2<T>::unpack(clw[i]), c2 = Pack2<T>::unpack(chw[i]);
+    const float2 s1v = Pack2<T>::unpack(slw[i]), s2v = Pack2<T>::unpack(shw[i]);
+    ol[i] = Pack2<T>::run(x1.x * c1.x - x2.x * s1v.x, x1.y * c1.y - x2.y * s1v.y);
+    oh[i] = Pack2<T>::run(x2.x * c2.x + x1.x * s2v.x, x2.y * c2.y + x1.y * s2v.y);
+  }
+  *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+  *reinterpret_cast<uint4*>(dst + D / 2 + c * 8) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+}
+
+template <typename T, int D>
+int launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st) {
+  RotateJob jq{p.q, q_out, p.q_stride[0], p.q_stride[1], p.q_stride[2], p.H_q, p.N_q,
+               (int64_t)p.B * p.H_q * p.N_q * (D / 16)};
+  RotateJob jk{p.k, k_out, p.k_stride[0], p.k_stride[1], p.k_stride[2], p.H_kv, p.N_kv,
+               (int64_t)p.B * p.H_kv * p.N_kv * (D / 16)};
+  const int64_t total = jq.chunks + jk.chunks;
+  rope_prepass_kernel<T, D><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      jq, jk, reinterpret_cast<const T*>(p.cos), reinterpret_cast<const T*>(p.sin), p.rope_stride_n);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "rope_prepass launch");
+}
+
+}  // namespace
+
+// Bytes of workspace with which af_fwd rotates Q and K once up front (one extra HBM-bound
+// launch) instead of inside the attention kernel, where every query tile re-rotates every K
+// tile it visits: O(N_q/128 * group) rotations per key against one.
+static int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
+
+int64_t fwd_tcgen05_workspace_bytes(const AfProblem& p) {
+  if (!p.rope) return 0;
+  const int64_t q_tiles_per_kv_head = (int64_t)((p.N_q + tc::BM - 1) / tc::BM) * (p.H_q / p.H_kv);
+  if (q_tiles_per_kv_head < 4) return 0;   // short sequences: rotate in shared memory, one launch
+  return align256((int64_t)p.B * p.H_q * p.N_q * p.D * 2) + align256((int64_t)p.B * p.H_kv * p.N_kv * p.D * 2);
+}
+
+bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_stride, const char** why) {
+  auto no = [&](const char* w) { if (why) *why = w; return false; };
+  if (p.dtype != AF_F16 && p.dtype != AF_BF16) return no("dtype is not f16/bf16");
+  if (p.D != 64 && p.D != 128) return no("head_dim is not 64 or 128");
+  if (p.norm_kind != AF_NORM_SOFTMAX) return no("normalisation is not softmax");
+  if (p.bias_kind == AF_BIAS_ADDITIVE) return no("additive bias");
+  if (!(p.sm_scale > 0.f)) return no("non-positive scale");
+  if (p.N_q < 1 || p.N_kv < 1) return no("empty sequence");
+  if (p.mask_kind == AF_MASK_BLOCKS && (p.block_m % tc::BM != 0 || p.block_n % tc::BN != 0))
+    return no("block size is not a multiple of 128");
+  if (!tma_ok(p.q, p.B, p.H_q, p.N_q, p.q_stride) || !tma_ok(p.k, p.B, p.H_kv, p.N_kv, p.k_stride) ||
+      !tma_ok(p.v, p.B, p.H_kv, p.N_kv, p.v_stride))
+    return no("Q/K/V not TMA-addressable (16-byte aligned base and strides, unit inner stride)");
+  if (o_stride[3] != 1 || ((uintptr_t)o & 15) != 0 || o_stride[2] % 8 != 0 || o_stride[1] % 8 != 0 ||
+      o_stride[0] % 8 != 0)
+    return no("O rows not 16-byte aligned");
+  if (p.rope && (p.rope_stride_n % 8 != 0 || ((uintptr_t)p.cos & 15) != 0 || ((uintptr_t)p.sin & 15) != 0))
+    return no("cos/sin rows not 16-byte aligned");
+  return true;
+}
+
+int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
+  const char* why = nullptr;
+  if (!fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why))
+    return fail(AF_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+  const AfProblem& p = a.p;
+  tc::TcArgs args;
+  args.a = a;
+  args.num_m_blocks = (p.N_q + tc::BM - 1) / tc::BM;
+  args.kv_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_n / tc::BN : 1;
+  args.q_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_m / tc::BM : 1;
+  AF_REQUIRE((int64_t)args.num_m_blocks * p.B * p.H_q <= 0x7fffffff, "too many tiles for one launch");
+
+  int mode = p.rope ? tc::ROPE_FUSED : tc::ROPE_NONE;
+  const void* q_ptr = p.q;
+  const void* k_ptr = p.k;
+  int64_t q_stride[4] = {p.q_stride[0], p.q_stride[1], p.q_stride[2], p.q_stride[3]};
+  int64_t k_stride[4] = {p.k_stride[0], p.k_stride[1], p.k_stride[2], p.k_stride[3]};
+  const int64_t need = fwd_tcgen05_workspace_bytes(p);
+  if (p.rope && need > 0 && a.workspace != nullptr && a.workspace_bytes >= need &&
+      ((uintptr_t)a.workspace & 255) == 0) {
+    void* q_rot = a.workspace;
+    void* k_rot = static_cast<char*>(a.workspace) + align256((int64_t)p.B * p.H_q * p.N_q * p.D * 2);
+    int rc;
+    if (p.dtype == AF_F16)
+      rc = p.D == 64 ? launch_prepass<__half, 64>(p, q_rot, k_rot, st) : launch_prepass<__half, 128>(p, q_rot, k_rot, st);
+    else
+      rc = p.D == 64 ? launch_prepass<__nv_bfloat16, 64>(p, q_rot, k_rot, st)
+                     : launch_prepass<__nv_bfloat16, 128>(p, q_rot, k_rot, st);
+    if (rc != AF_OK) return rc;
+    mode = tc::ROPE_NONE;   // operands are rotated: run the plain kernel on them
+    q_ptr = q_rot; k_ptr = k_rot;
+    q_stride[3] = 1; q_stride[2] = p.D; q_stride[1] = (int64_t)p.N_q * p.D; q_stride[0] = q_stride[1] * p.H_q;
+    k_stride[3] = 1; k_stride[2] = p.D; k_stride[1] = (int64_t)p.N_kv * p.D; k_stride[0] = k_stride[1] * p.H_kv;
+  }
+
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, p.dtype, q_ptr, p.B, p.H_q, p.N_q, p.D, q_stride)) != AF_OK) return rc;
+  if ((rc = make_map(&mk, p.dtype, k_ptr, p.B, p.H_kv, p.N_kv, p.D, k_stride)) != AF_OK) return rc;
+  if ((rc = make_map(&mv, p.dtype, p.v, p.B, p.H_kv, p.N_kv, p.D, p.v_stride)) != AF_OK) return rc;
+  if (p.D == 64) {
+    if (mode == tc::ROPE_NONE) return tc::launch_d64_norope(p.dtype, args, mq, mk, mv, st);
+    return tc::launch_d64_fused(p.dtype, args, mq, mk, mv, st);
+  }
+  if (mode == tc::ROPE_NONE) return tc::launch_d128_norope(p.dtype, args, mq, mk, mv, st);
+  return tc::launch_d128_fused(p.dtype, args, mq, mk, mv, st);
+}
+
+}  // namespace af

@@ -47,18 +47,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
+constexpr long long kWaitLimitCycles = 1ll << 32;  // ~2 s of SM clocks: far beyond any legitimate wait
 
 // Wait for the phase with the given parity.  Returns false if `*abort_flag` was raised by
-// another role of the CTA or the time limit passed (in which case the flag is raised here).
+// another role of the CTA or the cycle limit passed (in which case the flag is raised here).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         return false;
       }

@@ -46,7 +46,8 @@ class AfProblem(C.Structure):
 
 
 class AfFwdParams(C.Structure):
-    _fields_ = [("p", AfProblem), ("o", PTR), ("o_stride", S4), ("lse", PTR), ("lse_stride", S3)]
+    _fields_ = [("p", AfProblem), ("o", PTR), ("o_stride", S4), ("lse", PTR), ("lse_stride", S3),
+                ("workspace", PTR), ("workspace_bytes", I64)]
 
 
 class AfBwdParams(C.Structure):
@@ -77,7 +78,7 @@ class AfDecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("af_fwd", "af_bwd", "af_decode_split", "af_decode_combine",
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_decode_split", "af_decode_combine",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -101,6 +102,8 @@ def load() -> C.CDLL:
                 "(there is no fallback path)")
         lib = C.CDLL(str(LIB_PATH))
         lib.af_fwd.argtypes = [C.POINTER(AfFwdParams), PTR]
+        lib.af_fwd_workspace_bytes.argtypes = [C.POINTER(AfFwdParams)]
+        lib.af_fwd_workspace_bytes.restype = I64
         lib.af_bwd.argtypes = [C.POINTER(AfBwdParams), PTR]
         lib.af_decode_split.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine.argtypes = [C.POINTER(AfDecodeParams), PTR]

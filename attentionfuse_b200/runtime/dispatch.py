@@ -109,6 +109,10 @@ def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, 
     params.o, params.o_stride = out.data_ptr(), _lib.strides(out)
     if save_lse is not None:
         params.lse, params.lse_stride = save_lse.data_ptr(), _lib.strides(save_lse, 3)
+    need = int(lib.af_fwd_workspace_bytes(C.byref(params)))
+    if need > 0 and os.environ.get("ATTNFUSE_ROPE_IN_KERNEL", "0") != "1":
+        workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
+        params.workspace, params.workspace_bytes = workspace.data_ptr(), need
     with torch.cuda.device(Q.device):
         rc = lib.af_fwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_fwd")

@@ -87,6 +87,8 @@ typedef struct AfFwdParams {
   AfProblem p;
   void*   o;   int64_t o_stride[4];    /* (B, H_q, N_q, D), caller allocated               */
   float*  lse; int64_t lse_stride[3];  /* (B, H_q, N_q) fp32 log-sum-exp, or NULL          */
+  void*   workspace;                   /* optional scratch, see af_fwd_workspace_bytes     */
+  int64_t workspace_bytes;
 } AfFwdParams;
 
 typedef struct AfBwdParams {
@@ -127,6 +129,13 @@ typedef struct AfDecodeParams {
  * and, with mask_kind == AF_MASK_BLOCKS, the one in run_block_sparse
  * (attnfuse/runtime/block_mask.py:246-270). */
 AF_API int af_fwd(const AfFwdParams* params, af_stream_t stream);
+
+/* Scratch bytes with which af_fwd runs fastest for this problem (0: none needed).  Only RoPE
+ * problems with many query tiles per KV head use scratch: K is then rotated once into it
+ * instead of once per query tile.  Without (enough) workspace af_fwd rotates K inside the
+ * kernel, in shared memory, and gives the same result.  No counterpart in the reference, whose
+ * kernel always re-rotates each K tile (attnfuse/compiler/codegen.py:332-341).  Host only. */
+AF_API int64_t af_fwd_workspace_bytes(const AfFwdParams* params);
 
 /* Replaces the three launches of run_backward (attnfuse/runtime/backward.py:131-190:
  * preproc, dK/dV, dQ) and of run_block_sparse_backward

@@ -232,3 +232,22 @@ def test_lse_output():
         run_attention(graph, Q.to(DEV), K.to(DEV), V.to(DEV), save_lse=L, family=fam)
         _, want = orc.attention(Q, K, V, causal=True, return_lse=True)
         assert (L.cpu() - want).abs().max().item() < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rope_prepass_and_in_kernel_rotation_agree(D, dtype, monkeypatch):
+    """Long sequences rotate Q and K once in a pre-pass (caller workspace); short ones, or callers
+    that pass no workspace, rotate inside the kernel in shared memory.  Same arithmetic, same bits."""
+    B, Hq, Hkv, N = 1, 8, 2, 1000
+    Q, K, V = qkv(900, B, Hq, Hkv, N, N, D, dtype)
+    cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    want = orc.attention(Q, K, V, causal=True, cos=cos, sin=sin)
+    monkeypatch.setenv("ATTNFUSE_ROPE_IN_KERNEL", "0")
+    pre = causal_rope(q, k, v, cos=cos.to(DEV), sin=sin.to(DEV))
+    monkeypatch.setenv("ATTNFUSE_ROPE_IN_KERNEL", "1")
+    fused = causal_rope(q, k, v, cos=cos.to(DEV), sin=sin.to(DEV))
+    assert_close(pre, want, dtype, what="pre-pass")
+    assert_close(fused, want, dtype, what="in-kernel")
+    assert torch.equal(pre, fused)
