@@ -405,12 +405,7 @@ int launch_one(const AfBwdParams& a, cudaStream_t st) {
   AF_CUDA_OK(cudaFuncSetAttribute(kdkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   AF_CUDA_OK(cudaFuncSetAttribute(kdq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
-  const int64_t rows = (int64_t)p.B * p.H_q * p.N_q;
-  if (rows > 0) {
-    bwd_delta_kernel<T><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(a);
-    count_launch();
-    AF_CUDA_OK(cudaGetLastError());
-  }
+  { const int rc = launch_bwd_delta(a, st); if (rc != AF_OK) return rc; }
   int subs_n = 1, subs_m = 1, n_tiles, m_tiles;
   if (p.mask_kind == AF_MASK_BLOCKS) {
     subs_n = (p.block_n + BT - 1) / BT;
@@ -442,6 +437,21 @@ int launch_dtype(const AfBwdParams& a, cudaStream_t st) {
 }
 
 }  // namespace
+
+// delta = rowsum(dO * O), fp32 (B, H_q, N_q); shared by both backward families.
+int launch_bwd_delta(const AfBwdParams& a, cudaStream_t st) {
+  const int64_t rows = (int64_t)a.p.B * a.p.H_q * a.p.N_q;
+  if (rows <= 0) return AF_OK;
+  const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
+  switch (a.p.dtype) {
+    case AF_F16: bwd_delta_kernel<__half><<<blocks, 256, 0, st>>>(a); break;
+    case AF_BF16: bwd_delta_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(a); break;
+    case AF_F32: bwd_delta_kernel<float><<<blocks, 256, 0, st>>>(a); break;
+    default: return fail(AF_ERR_INVALID, "unknown dtype %d", a.p.dtype);
+  }
+  count_launch();
+  return check_cuda(cudaGetLastError(), "bwd_delta launch");
+}
 
 int launch_bwd_ffma(const AfBwdParams& a, cudaStream_t st) {
   switch (a.p.dtype) {

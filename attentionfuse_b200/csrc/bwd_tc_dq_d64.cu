@@ -1,0 +1,9 @@
+// Instantiations of the tcgen05 backward kernel: MODE_DQ, head_dim 64, both half precision
+// element types, every (causal, ALiBi, RoPE) composition.
+#include "bwd_tcgen05.cuh"
+
+namespace af {
+namespace tcb {
+AF_DEFINE_BWD_UNIT(launch_dq_d64, 64, MODE_DQ)
+}  // namespace tcb
+}  // namespace af

@@ -1,0 +1,500 @@
+// Backward attention on tcgen05 + TMEM: dK/dV (key-stationary) and dQ (query-stationary).
+//
+// Replaces the reference backward kernels (attnfuse/compiler/codegen_backward.py:75-302 and the
+// block-sparse pair, attnfuse/compiler/codegen_blocksparse_bwd.py:29-233) for f16/bf16 inputs with
+// head_dim 64 or 128.  Same two-pass structure as the reference -- no atomics, dK/dV of a GQA
+// group are summed inside the CTA that owns the key tile -- with the recompute on tensor cores:
+//
+//   MODE_DKV  one CTA owns 128 keys of one (batch, kv head): K_j, V_j stay in shared memory,
+//             64-row tiles of Q_i and dO_i stream through a TMA ring, for every query head of
+//             the group.  Scores are computed TRANSPOSED, S^T = K_j Q_i^T and dP^T = V_j dO_i^T
+//             (TMEM lane = key), so that P^T and dS^T, written back to TMEM as f16/bf16, are
+//             directly the A operands of  dV_j += P^T dO_i  and  dK_j += dS^T Q_i.
+//   MODE_DQ   one CTA owns 128 query rows of one (batch, query head): Q_i, dO_i stay, 64-key
+//             tiles of K_j, V_j stream;  S = Q_i K_j^T, dP = dO_i V_j^T (TMEM lane = query row),
+//             dS goes back to TMEM and feeds  dQ_i += dS K_j.
+//
+// P = exp2(S*scale*log2e - L*log2e) with L the log-sum-exp saved by the forward;
+// dS = P * (dP - delta), delta = rowsum(dO * O); dK and dQ are multiplied by the scale at the
+// end (codegen_backward.py:161-191).  With RoPE the operands are the pre-rotated Q', K' and the
+// epilogue applies the transpose of the rotation to dQ', dK' while they are still fp32.
+// S^T/dP^T (or S/dP) are double-buffered in TMEM so the MMA warp computes step i+1 while the
+// 128 element-wise threads work on step i.  All waits are bounded.
+#pragma once
+#include "fwd_tcgen05.cuh"
+
+namespace af {
+namespace tcb {
+
+using namespace ptx;
+using tc::Pack2;
+using tc::ex2_approx;
+
+enum { MODE_DKV = 0, MODE_DQ = 1 };
+enum { EMASK_NONE = 0, EMASK_CAUSAL = 1 };
+
+constexpr int BS = 128;   // rows of the stationary operands (TMEM lanes)
+constexpr int BT = 64;    // rows of a streamed tile (columns of S per step)
+
+template <int D> struct BCfg {
+  static constexpr int PANELS = D / 64;
+  static constexpr int STAT_PANEL = BS * 128;               // bytes of a 128-row, 64-element panel
+  static constexpr int STRM_PANEL = BT * 128;
+  static constexpr int STAT_TILE = PANELS * STAT_PANEL;
+  static constexpr int STRM_TILE = PANELS * STRM_PANEL;
+  static constexpr int STAGES = 3;
+  static constexpr int STATS_BYTES = 2 * BT * 4;            // L*log2e and delta of a streamed tile
+  static constexpr int SMEM_BYTES = 2 * STAT_TILE + STAGES * (2 * STRM_TILE + STATS_BYTES) + 1024 + 512;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_X0 = 0, COL_Y0 = 64, COL_X1 = 128, COL_Y1 = 192, COL_ACC1 = 256, COL_ACC2 = 256 + D;
+};
+
+struct BBarriers {
+  uint64_t stat_full;
+  uint64_t strm_full[4], strm_empty[4];
+  uint64_t xy_full[2], p_full[2], acc_done[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdArgs {
+  AfBwdParams a;
+  int tiles;            // stationary tiles along the sequence
+  int steps_per_block;  // block lists: streamed 64-row steps per listed block
+  int stat_per_block;   // block lists: stationary 128-row tiles per block
+};
+
+// The streamed steps one stationary tile visits for one head.
+struct StepWalk {
+  int cnt, first;
+  const int32_t* list;
+  int per, block;
+  __device__ __forceinline__ int row0(int s) const {
+    if (list != nullptr) return list[s / per] * block + (s % per) * BT;
+    return (first + s) * BT;
+  }
+};
+
+template <int MODE>
+__device__ __forceinline__ StepWalk make_steps(const AfProblem& p, const BwdArgs& args, int tile, int h) {
+  StepWalk w;
+  w.list = nullptr; w.per = 1; w.block = BT; w.first = 0;
+  const int t0 = tile * BS;
+  if (p.mask_kind == AF_MASK_BLOCKS) {
+    const int blk = tile / args.stat_per_block;
+    w.per = args.steps_per_block;
+    if (MODE == MODE_DKV) {
+      w.block = p.block_m;
+      w.list = p.q_idx + (int64_t)h * p.q_idx_stride_h + (int64_t)blk * p.q_idx_stride_k;
+      w.cnt = p.q_num[(int64_t)h * p.q_num_stride_h + blk] * w.per;
+    } else {
+      w.block = p.block_n;
+      w.list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)blk * p.kv_idx_stride_q;
+      w.cnt = p.kv_num[(int64_t)h * p.kv_num_stride_h + blk] * w.per;
+    }
+  } else if (MODE == MODE_DKV) {
+    const int total = (p.N_q + BT - 1) / BT;
+    w.first = (p.mask_kind == AF_MASK_CAUSAL) ? t0 / BT : 0;     // query rows >= first key of the tile
+    w.cnt = total - w.first;
+  } else {
+    const int hi = (p.mask_kind == AF_MASK_CAUSAL) ? min(min(t0 + BS, p.N_q), p.N_kv) : p.N_kv;
+    w.cnt = (hi + BT - 1) / BT;
+  }
+  if (w.cnt < 0) w.cnt = 0;
+  return w;
+}
+
+template <typename T, int D, int MODE, int EMASK, bool ALIBI, bool ROPE>
+__global__ void __launch_bounds__(192, 1)
+bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a1,
+                   const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b1,
+                   const __grid_constant__ CUtensorMap map_b2) {
+  using C = BCfg<D>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int AB_FMT = (Elem<T>::code == AF_BF16) ? 1 : 0;
+  constexpr uint32_t IDESC_XY = umma_idesc_f16(AB_FMT, BS, BT, 0, 0);
+  constexpr uint32_t IDESC_ACC = umma_idesc_f16(AB_FMT, BS, D, 0, 1);
+  constexpr int STAGE_BYTES = 2 * C::STRM_TILE + C::STATS_BYTES;
+
+  const AfBwdParams& a = args.a;
+  const AfProblem& p = a.p;
+
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA1 = smem_base, sA2 = smem_base + C::STAT_TILE;
+  const uint32_t sStage0 = smem_base + 2 * C::STAT_TILE;
+  BBarriers* bars = reinterpret_cast<BBarriers*>(smem + 2 * C::STAT_TILE + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int group = p.H_q / p.H_kv;
+  const int heads_here = (MODE == MODE_DKV) ? p.H_kv : p.H_q;
+  const int bh_count = p.B * heads_here;
+  // heaviest tiles first: causal dK/dV work shrinks with the key tile index, dQ work grows with
+  // the query tile index
+  const int tile = (MODE == MODE_DQ && EMASK == EMASK_CAUSAL) ? (args.tiles - 1 - (int)(blockIdx.x / bh_count))
+                                                              : (int)(blockIdx.x / bh_count);
+  const int bh = blockIdx.x % bh_count;
+  const int b = bh / heads_here, hx = bh % heads_here;        // hx: kv head (DKV) or query head (DQ)
+  const int h_kv = (MODE == MODE_DKV) ? hx : hx / group;
+  const int t0 = tile * BS;
+  const int n_heads = (MODE == MODE_DKV) ? group : 1;
+
+  if (tid == 0) {
+    mbar_init(&bars->stat_full, 1);
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&bars->strm_full[s], 1);
+      mbar_init(&bars->strm_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->xy_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->acc_done[t], 1);
+    }
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+
+  // total number of steps of this CTA (all heads of the group in DKV mode)
+  int total_steps = 0;
+  for (int g = 0; g < n_heads; ++g)
+    total_steps += make_steps<MODE>(p, args, tile, (MODE == MODE_DKV) ? h_kv * group + g : hx).cnt;
+
+  if (warp == 4) {
+    // ============================== producer (TMA + per-step statistics) ==============================
+    if (total_steps > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_a2); tma_prefetch_desc(&map_b1); tma_prefetch_desc(&map_b2);
+        mbar_arrive_expect_tx(&bars->stat_full, 2 * C::STAT_TILE);
+        const int ha = (MODE == MODE_DKV) ? h_kv : hx;
+#pragma unroll
+        for (int pn = 0; pn < C::PANELS; ++pn) {
+          tma_load_4d(smem + pn * C::STAT_PANEL, &map_a1, &bars->stat_full, pn * 64, t0, ha, b);
+          tma_load_4d(smem + C::STAT_TILE + pn * C::STAT_PANEL, &map_a2, &bars->stat_full, pn * 64, t0, ha, b);
+        }
+      }
+      int it = 0;
+      bool ok = true;
+      for (int g = 0; g < n_heads && ok; ++g) {
+        const int h = (MODE == MODE_DKV) ? h_kv * group + g : hx;
+        const int hb = (MODE == MODE_DKV) ? h : h_kv;                 // head of the streamed tensors
+        const StepWalk w = make_steps<MODE>(p, args, tile, h);
+        for (int s = 0; s < w.cnt; ++s, ++it) {
+          const int st = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&bars->strm_empty[st], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          const int r0 = w.row0(s);
+          unsigned char* stage = smem + 2 * C::STAT_TILE + st * STAGE_BYTES;
+          if (MODE == MODE_DKV) {
+            // L*log2e and delta of the 64 streamed query rows; rows past N_q get (+inf, 0) so that
+            // their probabilities are exactly zero.
+            float* stats = reinterpret_cast<float*>(stage + 2 * C::STRM_TILE);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const int q = r0 + lane + 32 * k;
+              float l2 = INFINITY, dl = 0.f;
+              if (q < p.N_q) {
+                const float l = a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)q * a.lse_stride[2]];
+                l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+                dl = a.delta[((int64_t)b * p.H_q + h) * p.N_q + q];
+              }
+              stats[lane + 32 * k] = l2;
+              stats[BT + lane + 32 * k] = dl;
+            }
+            __syncwarp();
+          }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&bars->strm_full[st], 2 * C::STRM_TILE);
+#pragma unroll
+            for (int pn = 0; pn < C::PANELS; ++pn) {
+              tma_load_4d(stage + pn * C::STRM_PANEL, &map_b1, &bars->strm_full[st], pn * 64, r0, hb, b);
+              tma_load_4d(stage + C::STRM_TILE + pn * C::STRM_PANEL, &map_b2, &bars->strm_full[st], pn * 64, r0, hb, b);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ============================== MMA issuer ==============================
+    if (lane == 0 && total_steps > 0) {
+      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
+      tc_fence_after_sync();
+      auto issue_xy = [&](int it) -> bool {
+        const int st = it % STAGES, t = it & 1;
+        if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) return false;
+        if (it >= 2 && !mbar_wait(&bars->acc_done[t], ((it >> 1) - 1) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t b1 = sStage0 + st * STAGE_BYTES, b2 = b1 + C::STRM_TILE;
+        const uint32_t xt = tmem + (t ? C::COL_X1 : C::COL_X0), yt = tmem + (t ? C::COL_Y1 : C::COL_Y0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss(xt, umma_desc_sw128(sA1 + (kk >> 2) * C::STAT_PANEL + (kk & 3) * 32, 16, 1024),
+                  umma_desc_sw128(b1 + (kk >> 2) * C::STRM_PANEL + (kk & 3) * 32, 16, 1024), IDESC_XY, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_ss(yt, umma_desc_sw128(sA2 + (kk >> 2) * C::STAT_PANEL + (kk & 3) * 32, 16, 1024),
+                  umma_desc_sw128(b2 + (kk >> 2) * C::STRM_PANEL + (kk & 3) * 32, 16, 1024), IDESC_XY, kk > 0 ? 1u : 0u);
+        umma_commit(&bars->xy_full[t]);
+        return true;
+      };
+      if (ok) ok = issue_xy(0);
+      for (int it = 0; ok && it < total_steps; ++it) {
+        if (it + 1 < total_steps) ok = issue_xy(it + 1);
+        if (!ok) break;
+        const int st = it % STAGES, t = it & 1;
+        if (!mbar_wait(&bars->p_full[t], (it >> 1) & 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t b1 = sStage0 + st * STAGE_BYTES, b2 = b1 + C::STRM_TILE;
+        const uint32_t xt = tmem + (t ? C::COL_X1 : C::COL_X0), yt = tmem + (t ? C::COL_Y1 : C::COL_Y0);
+        // streamed tiles as N-major B operands: 16 rows per k-step (2048 B), panels LBO apart
+        if (MODE == MODE_DKV) {
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)      // dV += P^T dO
+            umma_ts(tmem + C::COL_ACC1, xt + kk * 8, umma_desc_sw128(b2 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)      // dK += dS^T Q
+            umma_ts(tmem + C::COL_ACC2, yt + kk * 8, umma_desc_sw128(b1 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)      // dQ += dS K
+            umma_ts(tmem + C::COL_ACC1, yt + kk * 8, umma_desc_sw128(b1 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->strm_empty[st]);
+        umma_commit(&bars->acc_done[t]);
+      }
+    }
+  } else if (warp < 4) {
+    // ============================== element-wise group / epilogue ==============================
+    const int srow = t0 + tid;                       // key (DKV) or query row (DQ) of this thread
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const float scale2 = p.sm_scale * kLog2e;
+    float l2_row = INFINITY, dl_row = 0.f;           // DQ mode: statistics of this thread's query row
+    if (MODE == MODE_DQ && srow < p.N_q) {
+      const float l = a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)hx * a.lse_stride[1] + (int64_t)srow * a.lse_stride[2]];
+      l2_row = (l == -INFINITY) ? INFINITY : l * kLog2e;
+      dl_row = a.delta[((int64_t)b * p.H_q + hx) * p.N_q + srow];
+    }
+    bool alive = true;
+    int it = 0;
+    for (int g = 0; g < n_heads && alive; ++g) {
+      const int h = (MODE == MODE_DKV) ? h_kv * group + g : hx;
+      const StepWalk w = make_steps<MODE>(p, args, tile, h);
+      const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
+      for (int s = 0; s < w.cnt; ++s, ++it) {
+        const int st = it % STAGES, t = it & 1;
+        const int r0 = w.row0(s);
+        if (MODE == MODE_DKV && !mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->xy_full[t], (it >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after_sync();
+        const uint32_t xt = tmem + lane_base + (t ? C::COL_X1 : C::COL_X0);
+        const uint32_t yt = tmem + lane_base + (t ? C::COL_Y1 : C::COL_Y0);
+        uint32_t xr[BT], yr[BT];
+        tmem_ld32(xt, &xr[0]); tmem_ld32(xt + 32, &xr[32]);
+        tmem_ld32(yt, &yr[0]); tmem_ld32(yt + 32, &yr[32]);
+        tmem_wait_ld();
+        const float* stats = reinterpret_cast<const float*>(smem + 2 * C::STAT_TILE + st * STAGE_BYTES + 2 * C::STRM_TILE);
+
+        // Tile-level: does any element of this 128 x 64 tile need masking?
+        //   DKV: lane = key srow, column c = query r0 + c;  DQ: lane = query srow, column c = key r0 + c.
+        const int col_limit = ((MODE == MODE_DKV) ? p.N_q : p.N_kv) - r0;     // columns c < col_limit exist
+        bool need_mask = col_limit < BT;
+        if (EMASK == EMASK_CAUSAL)
+          need_mask = need_mask || ((MODE == MODE_DKV) ? (r0 < t0 + BS - 1) : (r0 + BT - 1 > t0));
+        const int rel = srow - r0;   // DKV: query c kept iff c >= rel;  DQ: key c kept iff c <= rel
+
+        uint32_t pk[BT / 2], dk[BT / 2];
+#pragma unroll
+        for (int c = 0; c < BT; c += 2) {
+          float pe[2], de[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int cc = c + u;
+            const float l2 = (MODE == MODE_DKV) ? stats[cc] : l2_row;
+            const float dl = (MODE == MODE_DKV) ? stats[BT + cc] : dl_row;
+            float e = fmaf(__uint_as_float(xr[cc]), scale2, -l2);
+            if (ALIBI) e -= slope2 * fabsf((float)rel - (float)cc);
+            float pr = ex2_approx(e);
+            if (need_mask) {
+              bool keep = cc < col_limit;
+              if (EMASK == EMASK_CAUSAL) keep = keep && ((MODE == MODE_DKV) ? (cc >= rel) : (cc <= rel));
+              pr = keep ? pr : 0.f;
+            }
+            pe[u] = pr;
+            de[u] = pr * (__uint_as_float(yr[cc]) - dl);
+          }
+          pk[c >> 1] = Pack2<T>::run(pe[0], pe[1]);
+          dk[c >> 1] = Pack2<T>::run(de[0], de[1]);
+        }
+        if (MODE == MODE_DKV) tmem_st32(xt, pk);
+        tmem_st32(yt, dk);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&bars->p_full[t]);
+      }
+    }
+
+    // ---------------- epilogue ----------------
+    if (alive && total_steps > 0) {
+      const int last = total_steps - 1;
+      alive = mbar_wait(&bars->acc_done[last & 1], (last >> 1) & 1, abort_flag);
+      tc_fence_after_sync();
+    }
+    if (alive) {
+      const int n_rows = (MODE == MODE_DKV) ? p.N_kv : p.N_q;
+      const bool store = srow < n_rows;
+      // gradient of the stationary operand that carries the scale (dK or dQ), with the rotation undone
+      {
+        const uint32_t acc = tmem + lane_base + ((MODE == MODE_DKV) ? C::COL_ACC2 : C::COL_ACC1);
+        T* dst = (MODE == MODE_DKV)
+                     ? reinterpret_cast<T*>(a.dk) + (int64_t)b * a.dk_stride[0] + (int64_t)h_kv * a.dk_stride[1] + (int64_t)srow * a.dk_stride[2]
+                     : reinterpret_cast<T*>(a.dq) + (int64_t)b * a.dq_stride[0] + (int64_t)hx * a.dq_stride[1] + (int64_t)srow * a.dq_stride[2];
+        const T* cos_row = ROPE ? reinterpret_cast<const T*>(p.cos) + (int64_t)srow * p.rope_stride_n : nullptr;
+        const T* sin_row = ROPE ? reinterpret_cast<const T*>(p.sin) + (int64_t)srow * p.rope_stride_n : nullptr;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          // columns [32c, 32c+32) and their partners [32c + D/2, ...)
+          uint32_t lo[32], hi[32];
+          if (total_steps > 0) {
+            tmem_ld32(acc + c * 32, lo);
+            tmem_ld32(acc + D / 2 + c * 32, hi);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) lo[i] = hi[i] = 0u;
+          }
+          if (store) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              float gl[8], gh[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                gl[i] = __uint_as_float(lo[q4 * 8 + i]) * p.sm_scale;
+                gh[i] = __uint_as_float(hi[q4 * 8 + i]) * p.sm_scale;
+              }
+              if (ROPE) {
+                const int d0 = c * 32 + q4 * 8;
+                const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_row + d0));
+                const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_row + D / 2 + d0));
+                const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_row + d0));
+                const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_row + D / 2 + d0));
+                const uint32_t clw[4] = {cl.x, cl.y, cl.z, cl.w}, chw[4] = {ch.x, ch.y, ch.z, ch.w};
+                const uint32_t slw[4] = {sl.x, sl.y, sl.z, sl.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 c1 = Pack2<T>::unpack(clw[i]), c2 = Pack2<T>::unpack(chw[i]);
+                  const float2 s1 = Pack2<T>::unpack(slw[i]), s2 = Pack2<T>::unpack(shw[i]);
+                  const float a0 = gl[2 * i], a1 = gl[2 * i + 1], b0 = gh[2 * i], b1 = gh[2 * i + 1];
+                  // transpose of the rotation: g[d] = g'[d] cos[d] + g'[d+h] sin[d+h]; g[d+h] = g'[d+h] cos[d+h] - g'[d] sin[d]
+                  gl[2 * i] = a0 * c1.x + b0 * s2.x;     gl[2 * i + 1] = a1 * c1.y + b1 * s2.y;
+                  gh[2 * i] = b0 * c2.x - a0 * s1.x;     gh[2 * i + 1] = b1 * c2.y - a1 * s1.y;
+                }
+              }
+              uint4 vl, vh;
+              vl.x = Pack2<T>::run(gl[0], gl[1]); vl.y = Pack2<T>::run(gl[2], gl[3]);
+              vl.z = Pack2<T>::run(gl[4], gl[5]); vl.w = Pack2<T>::run(gl[6], gl[7]);
+              vh.x = Pack2<T>::run(gh[0], gh[1]); vh.y = Pack2<T>::run(gh[2], gh[3]);
+              vh.z = Pack2<T>::run(gh[4], gh[5]); vh.w = Pack2<T>::run(gh[6], gh[7]);
+              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = vl;
+              *reinterpret_cast<uint4*>(dst + D / 2 + c * 32 + q4 * 8) = vh;
+            }
+          }
+        }
+      }
+      if (MODE == MODE_DKV) {
+        T* dst = reinterpret_cast<T*>(a.dv) + (int64_t)b * a.dv_stride[0] + (int64_t)h_kv * a.dv_stride[1] + (int64_t)srow * a.dv_stride[2];
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (total_steps > 0) {
+            tmem_ld32(tmem + lane_base + C::COL_ACC1 + c * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (store) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              v.x = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 0]), __uint_as_float(o[q4 * 8 + 1]));
+              v.y = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 2]), __uint_as_float(o[q4 * 8 + 3]));
+              v.z = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 4]), __uint_as_float(o[q4 * 8 + 5]));
+              v.w = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 6]), __uint_as_float(o[q4 * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, AF_STATUS_WAIT_TIMEOUT);
+  if (warp == 4) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+template <typename T, int D, int MODE, int EMASK, bool ALIBI, bool ROPE>
+int launch_instance(const BwdArgs& args, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1,
+                    const CUtensorMap& b2, cudaStream_t st) {
+  auto kern = bwd_tcgen05_kernel<T, D, MODE, EMASK, ALIBI, ROPE>;
+  constexpr int smem = BCfg<D>::SMEM_BYTES;
+  static bool configured = false;
+  if (!configured) {
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const AfProblem& p = args.a.p;
+  const int64_t ctas = (int64_t)args.tiles * p.B * (MODE == MODE_DKV ? p.H_kv : p.H_q);
+  if (ctas <= 0) return AF_OK;
+  kern<<<(unsigned)ctas, 192, smem, st>>>(args, a1, a2, b1, b2);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "bwd_tcgen05 launch");
+}
+
+template <typename T, int D, int MODE>
+int launch_composition(const BwdArgs& args, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1,
+                       const CUtensorMap& b2, cudaStream_t st) {
+  const AfProblem& p = args.a.p;
+  const int key = (p.mask_kind == AF_MASK_CAUSAL ? 4 : 0) + (p.bias_kind == AF_BIAS_ALIBI ? 2 : 0) + (p.rope ? 1 : 0);
+  switch (key) {
+    case 0: return launch_instance<T, D, MODE, EMASK_NONE, false, false>(args, a1, a2, b1, b2, st);
+    case 1: return launch_instance<T, D, MODE, EMASK_NONE, false, true>(args, a1, a2, b1, b2, st);
+    case 2: return launch_instance<T, D, MODE, EMASK_NONE, true, false>(args, a1, a2, b1, b2, st);
+    case 3: return launch_instance<T, D, MODE, EMASK_NONE, true, true>(args, a1, a2, b1, b2, st);
+    case 4: return launch_instance<T, D, MODE, EMASK_CAUSAL, false, false>(args, a1, a2, b1, b2, st);
+    case 5: return launch_instance<T, D, MODE, EMASK_CAUSAL, false, true>(args, a1, a2, b1, b2, st);
+    case 6: return launch_instance<T, D, MODE, EMASK_CAUSAL, true, false>(args, a1, a2, b1, b2, st);
+    default: return launch_instance<T, D, MODE, EMASK_CAUSAL, true, true>(args, a1, a2, b1, b2, st);
+  }
+}
+
+int launch_dkv_d64(int dtype, const BwdArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_dkv_d128(int dtype, const BwdArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_dq_d64(int dtype, const BwdArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_dq_d128(int dtype, const BwdArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+
+#define AF_DEFINE_BWD_UNIT(NAME, DIM, MODE)                                                                   \
+  int NAME(int dtype, const BwdArgs& args, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1, \
+           const CUtensorMap& b2, cudaStream_t st) {                                                          \
+    if (dtype == AF_F16) return launch_composition<__half, DIM, MODE>(args, a1, a2, b1, b2, st);              \
+    return launch_composition<__nv_bfloat16, DIM, MODE>(args, a1, a2, b1, b2, st);                            \
+  }
+
+}  // namespace tcb
+}  // namespace af

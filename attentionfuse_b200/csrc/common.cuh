@@ -2,6 +2,7 @@
 // reporting, launch accounting and the per-family launcher prototypes.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -69,7 +70,16 @@ int64_t fwd_tcgen05_workspace_bytes(const AfProblem& p);
 bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_stride,
                           const char** why);
 
+// Shared host helpers of the tensor-core kernels (defined in fwd_tcgen05_host.cu).
+
+int tc_make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
+                int box_rows);
+bool tc_tma_ok(const void* ptr, int B, int H, int N, const int64_t* st);
+int tc_launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st);
+
 int launch_bwd_ffma(const AfBwdParams& a, cudaStream_t st);
+int launch_bwd_delta(const AfBwdParams& a, cudaStream_t st);
+int64_t bwd_mma_workspace_bytes(const AfBwdParams& a);
 int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st);
 bool bwd_mma_supports(const AfBwdParams& a, const char** why);
 

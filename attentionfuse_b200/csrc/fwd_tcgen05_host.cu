@@ -25,7 +25,8 @@ EncodeTiledFn encode_fn() {
 }
 
 // (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x 128 x 1 x 1.
-int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st) {
+int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
+             int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t esz = 2;
@@ -36,7 +37,7 @@ int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, 
   if (H == 1) sH = sN * (cuuint64_t)N;
   if (B == 1) sB = sH * (cuuint64_t)H;
   cuuint64_t strides[3] = {sN, sH, sB};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(out, dtype == AF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -115,6 +116,18 @@ int launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st
 
 }  // namespace
 
+int tc_make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
+                int box_rows) {
+  return make_map(out, dtype, ptr, B, H, N, D, st, box_rows);
+}
+bool tc_tma_ok(const void* ptr, int B, int H, int N, const int64_t* st) { return tma_ok(ptr, B, H, N, st); }
+int tc_launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st) {
+  if (p.dtype == AF_F16)
+    return p.D == 64 ? launch_prepass<__half, 64>(p, q_out, k_out, st) : launch_prepass<__half, 128>(p, q_out, k_out, st);
+  return p.D == 64 ? launch_prepass<__nv_bfloat16, 64>(p, q_out, k_out, st)
+                   : launch_prepass<__nv_bfloat16, 128>(p, q_out, k_out, st);
+}
+
 // Bytes of workspace with which af_fwd rotates Q and K once up front (one extra HBM-bound
 // launch) instead of inside the attention kernel, where every query tile re-rotates every K
 // tile it visits: O(N_q/128 * group) rotations per key against one.
@@ -170,12 +183,7 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
       ((uintptr_t)a.workspace & 255) == 0) {
     void* q_rot = a.workspace;
     void* k_rot = static_cast<char*>(a.workspace) + align256((int64_t)p.B * p.H_q * p.N_q * p.D * 2);
-    int rc;
-    if (p.dtype == AF_F16)
-      rc = p.D == 64 ? launch_prepass<__half, 64>(p, q_rot, k_rot, st) : launch_prepass<__half, 128>(p, q_rot, k_rot, st);
-    else
-      rc = p.D == 64 ? launch_prepass<__nv_bfloat16, 64>(p, q_rot, k_rot, st)
-                     : launch_prepass<__nv_bfloat16, 128>(p, q_rot, k_rot, st);
+    const int rc = tc_launch_prepass(p, q_rot, k_rot, st);
     if (rc != AF_OK) return rc;
     mode = tc::ROPE_NONE;   // operands are rotated: run the plain kernel on them
     q_ptr = q_rot; k_ptr = k_rot;

@@ -60,6 +60,7 @@ class AfBwdParams(C.Structure):
         ("dq", PTR), ("dq_stride", S4),
         ("dk", PTR), ("dk_stride", S4),
         ("dv", PTR), ("dv_stride", S4),
+        ("workspace", PTR), ("workspace_bytes", I64),
     ]
 
 
@@ -78,7 +79,7 @@ class AfDecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_decode_split", "af_decode_combine",
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -105,12 +106,14 @@ def load() -> C.CDLL:
         lib.af_fwd_workspace_bytes.argtypes = [C.POINTER(AfFwdParams)]
         lib.af_fwd_workspace_bytes.restype = I64
         lib.af_bwd.argtypes = [C.POINTER(AfBwdParams), PTR]
+        lib.af_bwd_workspace_bytes.argtypes = [C.POINTER(AfBwdParams)]
+        lib.af_bwd_workspace_bytes.restype = I64
         lib.af_decode_split.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
         lib.af_decode_num_splits.argtypes = [I32, I32, I32, I32]
         lib.af_query_family.argtypes = [C.POINTER(AfProblem), I32]
-        for name in ("af_fwd", "af_bwd", "af_decode_split", "af_decode_combine",
+        for name in ("af_fwd", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine",
                      "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
                      "af_abi_version"):
             getattr(lib, name).restype = I32

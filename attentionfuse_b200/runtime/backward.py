@@ -54,6 +54,10 @@ def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_ki
     params.dq, params.dq_stride = dQ.data_ptr(), _lib.strides(dQ)
     params.dk, params.dk_stride = dK.data_ptr(), _lib.strides(dK)
     params.dv, params.dv_stride = dV.data_ptr(), _lib.strides(dV)
+    need = int(lib.af_bwd_workspace_bytes(C.byref(params)))
+    if need > 0:
+        workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
+        params.workspace, params.workspace_bytes = workspace.data_ptr(), need
     with torch.cuda.device(Q.device):
         rc = lib.af_bwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_bwd")

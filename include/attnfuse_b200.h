@@ -100,6 +100,8 @@ typedef struct AfBwdParams {
   void* dq; int64_t dq_stride[4];     /* like q                                            */
   void* dk; int64_t dk_stride[4];     /* like k (summed over the query-head group)         */
   void* dv; int64_t dv_stride[4];
+  void*   workspace;                  /* optional scratch, see af_bwd_workspace_bytes      */
+  int64_t workspace_bytes;
 } AfBwdParams;
 
 /* Split-K decode (query length 1).  Workspaces are fp32:
@@ -141,6 +143,10 @@ AF_API int64_t af_fwd_workspace_bytes(const AfFwdParams* params);
  * preproc, dK/dV, dQ) and of run_block_sparse_backward
  * (attnfuse/runtime/block_mask.py:302-362).  dq/dk/dv are fully overwritten. */
 AF_API int af_bwd(const AfBwdParams* params, af_stream_t stream);
+
+/* Scratch bytes the tensor-core backward needs for this problem (0: none).  RoPE problems keep
+ * the rotated Q and K there; without it af_bwd runs the exact FFMA kernels.  Host only. */
+AF_API int64_t af_bwd_workspace_bytes(const AfBwdParams* params);
 
 /* Replaces the split launch of run_flash_decode (attnfuse/runtime/flash_decode.py:149-170). */
 AF_API int af_decode_split(const AfDecodeParams* params, af_stream_t stream);

@@ -102,3 +102,19 @@ def test_no_grad_path_and_unsupported_falls_through():
     q = Q.to(DEV).requires_grad_(True)
     out = relu(q, K.to(DEV), V.to(DEV))       # no backward for ReLU: inference path, no graph
     assert not out.requires_grad
+
+
+@pytest.mark.parametrize("variant", ["causal", "causal_rope", "causal_alibi"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_backward_ffma_family_on_half_types(variant, dtype, monkeypatch):
+    """The exact FFMA kernels also serve half-precision inputs (forced here); both families must
+    meet the same bar."""
+    monkeypatch.setenv("ATTNFUSE_FAMILY", "1")
+    check(variant, (1, 4, 2, 150, 64), dtype)
+
+
+@pytest.mark.parametrize("variant", ["dense", "causal", "causal_rope"])
+@pytest.mark.parametrize("shape", [(1, 8, 2, 1024, 128), (2, 4, 4, 700, 64), (1, 2, 1, 129, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_backward_tcgen05_longer(variant, shape):
+    check(variant, shape, torch.bfloat16)
