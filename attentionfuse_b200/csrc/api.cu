@@ -116,6 +116,11 @@ int af_decode_combine(const AfDecodeParams* params, af_stream_t stream) {
   return launch_decode_combine(*params, static_cast<cudaStream_t>(stream));
 }
 
+int af_decode_static(const AfDecodeParams* params, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  return launch_decode_static(*params, static_cast<cudaStream_t>(stream));
+}
+
 int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int32_t H_q, int32_t D, int32_t dtype,
                                void* o, const int64_t o_stride[4], af_stream_t stream) {
   return launch_decode_combine_gathered(gathered, G, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));

@@ -85,6 +85,7 @@ bool bwd_mma_supports(const AfBwdParams& a, const char** why);
 
 int launch_decode_split(const AfDecodeParams& a, cudaStream_t st);
 int launch_decode_combine(const AfDecodeParams& a, cudaStream_t st);
+int launch_decode_static(const AfDecodeParams& a, cudaStream_t st);
 int launch_decode_combine_gathered(const float* gathered, int G, int B, int H_q, int D,
                                    int dtype, void* o, const int64_t* o_stride, cudaStream_t st);
 

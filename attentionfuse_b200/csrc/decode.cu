@@ -15,6 +15,8 @@
 //   * Partial results go to fp32 workspaces; a vectorised combine kernel merges the splits.
 //
 // Per-sequence valid lengths (kv_lens) are an extension: the reference only has a scalar N_KV.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace af {
@@ -431,6 +433,66 @@ int validate_decode(const AfDecodeParams& a) {
 }
 
 }  // namespace
+
+// ---------------------------------------------------------------------------------------
+// Decode without any allocation: the split-K partials live in a fixed array in device memory
+// that is part of the library image, so a caller that may not (or cannot) call cudaMalloc --
+// a serving loop that has handed all device memory to its own pool, code running inside a
+// region where the allocator must not be touched, a plugin host that only passes input and
+// output buffers -- can still decode.  Every GPU that loads the library holds the array
+// (AF_DECODE_STATIC_SCRATCH_BYTES) until the process exits.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchFloats = AF_DECODE_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+// Device address of the array on the current device.  In host code the symbol's name is only a
+// stand-in, so the address is looked up once per device with cudaGetSymbolAddress (the device
+// must be current) and cached.
+static int static_scratch_address(float** out) {
+  static std::mutex mu;
+  static float* cached[64] = {};
+  int dev = 0;
+  AF_CUDA_OK(cudaGetDevice(&dev));
+  AF_REQUIRE(dev >= 0 && dev < 64, "device index %d outside the cache of scratch addresses", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    AF_CUDA_OK(cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    AF_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    cached[dev] = static_cast<float*>(ptr);
+  }
+  *out = cached[dev];
+  return AF_OK;
+}
+
+int launch_decode_static(const AfDecodeParams& in, cudaStream_t st) {
+  AfDecodeParams a = in;
+  if (a.num_splits <= 0) {
+    int dev = 0, sms = 0;
+    AF_CUDA_OK(cudaGetDevice(&dev));
+    AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    a.num_splits = af_decode_num_splits(a.B, a.H_kv, a.N_kv, sms);
+  }
+  AF_REQUIRE(a.B > 0 && a.H_q > 0 && a.D > 0, "bad sizes");
+  const size_t rows = (size_t)a.num_splits * a.B * a.H_q;
+  const size_t need = rows * ((size_t)a.D + 2);
+  if (need > kStaticScratchFloats)
+    return fail(AF_ERR_WORKSPACE,
+                "af_decode_static: num_splits*B*H_q*(D+2) = %zu floats exceeds the built-in scratch of %zu floats "
+                "(%d bytes); use af_decode_split/af_decode_combine with caller workspaces",
+                need, (size_t)kStaticScratchFloats, (int)AF_DECODE_STATIC_SCRATCH_BYTES);
+  float* base = nullptr;
+  int rc = static_scratch_address(&base);
+  if (rc != AF_OK) return rc;
+  // Layout: m[rows], l[rows], acc[rows][D].  The split kernel writes every row of all three
+  // (empty splits write m = -inf, l = 0, acc = 0), so nothing left by an earlier call is read
+  // and nothing needs clearing.
+  a.ws_m = base;
+  a.ws_l = base + rows;
+  a.ws_acc = base + 2 * rows;
+  if ((rc = launch_decode_split(a, st)) != AF_OK) return rc;
+  return launch_decode_combine(a, st);
+}
 
 int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
   int rc = validate_decode(a);

@@ -79,7 +79,7 @@ class AfDecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine",
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine", "af_decode_static",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -110,6 +110,8 @@ def load() -> C.CDLL:
         lib.af_bwd_workspace_bytes.restype = I64
         lib.af_decode_split.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine.argtypes = [C.POINTER(AfDecodeParams), PTR]
+        lib.af_decode_static.argtypes = [C.POINTER(AfDecodeParams), PTR]
+        lib.af_decode_static.restype = I32
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
         lib.af_decode_num_splits.argtypes = [I32, I32, I32, I32]
         lib.af_query_family.argtypes = [C.POINTER(AfProblem), I32]

@@ -155,6 +155,29 @@ AF_API int af_decode_split(const AfDecodeParams* params, af_stream_t stream);
  * Writes o (if non-NULL) and partial (if non-NULL). */
 AF_API int af_decode_combine(const AfDecodeParams* params, af_stream_t stream);
 
+/* Decode (split + combine) for callers that cannot allocate device memory.  No counterpart in
+ * the reference, whose decode path allocates three fp32 workspaces per call with torch.empty.
+ *
+ * Who needs it: a host that owns the whole device memory through its own pool and forbids
+ * cudaMalloc afterwards, code on a path where the allocator must stay untouched, or a plugin
+ * interface that hands over nothing but input and output pointers.  Here the split-K partials
+ * go to a fixed array of AF_DECODE_STATIC_SCRATCH_BYTES that is part of the library image (each
+ * GPU that loads the library keeps it until the process ends); the call itself performs no
+ * cudaMalloc / cudaFree and calls no allocating library routine.
+ *
+ * params: as for af_decode_split + af_decode_combine; ws_m / ws_l / ws_acc are ignored, and
+ * num_splits <= 0 lets the library pick.  The problem must satisfy
+ *     num_splits * B * H_q * (D + 2) * 4 bytes <= AF_DECODE_STATIC_SCRATCH_BYTES,
+ * otherwise AF_ERR_WORKSPACE is returned and nothing is launched.
+ *
+ * The first call on each device looks up the array's device address (the device must be
+ * current); make that first call before starting any stream capture.  All calls share the one
+ * array: two calls whose kernels may overlap on the GPU (different streams, no ordering) race
+ * on it -- order them.  The array keeps the previous call's partials; every call overwrites all
+ * the rows it later reads, so no clearing is required between calls. */
+#define AF_DECODE_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+AF_API int af_decode_static(const AfDecodeParams* params, af_stream_t stream);
+
 /* KV-sharded decode: merge G per-rank partials [G, B, H_q, D+1] (normalised O, LSE) that an
  * all-gather placed in this GPU's own memory.  No counterpart in the reference, which is
  * single-GPU. */
