@@ -1,0 +1,71 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol the header
+declares, and the ctypes structures have the sizes the C compiler gives the header's structs."""
+import ctypes as C
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from attentionfuse_b200.runtime import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "attnfuse_b200.h"
+
+
+def declared_functions():
+    text = HEADER.read_text()
+    return sorted(set(re.findall(r"AF_API\s+[\w\s\*]+?\b(af_\w+)\s*\(", text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_functions()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert sorted(_lib.EXPORTS) == names
+    assert lib.af_abi_version() == 1
+    assert lib.af_launch_count() >= 0
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    src = tmp_path / "sizes.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "attnfuse_b200.h"\n'
+        "int main(void) {\n"
+        '  printf("%zu %zu %zu %zu\\n", sizeof(AfProblem), sizeof(AfFwdParams), sizeof(AfBwdParams), sizeof(AfDecodeParams));\n'
+        '  printf("%zu %zu %zu %zu %zu\\n", offsetof(AfProblem, q), offsetof(AfProblem, status), offsetof(AfFwdParams, workspace),\n'
+        "         offsetof(AfBwdParams, dv), offsetof(AfDecodeParams, partial));\n"
+        "  return 0;\n}\n")
+    exe = tmp_path / "sizes"
+    subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    sizes = [int(x) for x in out]
+    assert sizes[:4] == [C.sizeof(_lib.AfProblem), C.sizeof(_lib.AfFwdParams), C.sizeof(_lib.AfBwdParams),
+                         C.sizeof(_lib.AfDecodeParams)]
+    assert sizes[4:] == [_lib.AfProblem.q.offset, _lib.AfProblem.status.offset, _lib.AfFwdParams.workspace.offset,
+                         _lib.AfBwdParams.dv.offset, _lib.AfDecodeParams.partial.offset]
+
+
+def test_host_only_entry_points():
+    lib = _lib.load()
+    assert lib.af_decode_num_splits(16, 8, 32768, 148) == 3
+    assert lib.af_decode_num_splits(1, 8, 32768, 148) == 37
+    assert lib.af_decode_num_splits(1, 1, 300, 148) == 1
+    assert lib.af_decode_num_splits(64, 8, 1024, 148) == 1
+    # invalid arguments are refused on the host, before any CUDA call
+    params = _lib.AfFwdParams()
+    params.p.dtype = 7
+    assert lib.af_fwd(C.byref(params), None) == -1
+    assert "dtype" in _lib.last_error()
+    assert lib.af_fwd(None, None) == -1
+    assert lib.af_decode_static(None, None) == -1
+
+
+def test_missing_library_is_loud(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(_lib.AttnFuseLibraryError, match="no fallback"):
+        _lib.load()
