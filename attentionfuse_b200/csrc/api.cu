@@ -126,12 +126,18 @@ int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int3
   return launch_decode_combine_gathered(gathered, G, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));
 }
 
-int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count) {
-  // One CTA per (split, batch, kv head).  Aim for about two waves of CTAs over the SMs, keep at
-  // least 512 keys per split so the pipeline prologue amortises, cap at 64.
+int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count) {
+  // One CTA per (split, batch, kv head), two CTAs resident per SM.  Bandwidth-bound groups
+  // (<= 16 query heads per KV head) want about five waves of CTAs so that the ragged tail of
+  // per-sequence lengths averages out; the tensor-bound MQA case wants one wave.  Keep at least
+  // 512 keys per split so the pipeline prologue amortises; cap at 64.
   if (sm_count <= 0) sm_count = 148;
-  const int64_t units = (int64_t)(B > 0 ? B : 1) * (H_kv > 0 ? H_kv : 1);
-  int64_t want = (2LL * sm_count + units - 1) / units;
+  if (B < 1) B = 1;
+  if (H_kv < 1) H_kv = 1;
+  const int group = H_q > H_kv ? H_q / H_kv : 1;
+  const int64_t units = (int64_t)B * H_kv * ((group + 63) / 64);
+  const int64_t slots = 2LL * sm_count * (group > 16 ? 1 : 5);
+  int64_t want = (slots + units - 1) / units;
   const int64_t cap = N_kv / 512 > 1 ? N_kv / 512 : 1;
   if (want > cap) want = cap;
   if (want > 64) want = 64;

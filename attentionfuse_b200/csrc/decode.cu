@@ -5,7 +5,7 @@
 // (split, batch, kv head) and serves all query heads of the group from the same K/V tiles,
 // so the cache is streamed once per group rather than once per query head.
 //
-//   * K/V tiles of 64 keys are streamed with 16-byte cp.async into a 4-stage ring in shared
+//   * K/V tiles of 64 keys are streamed with 16-byte cp.async into a 3-stage ring in shared
 //     memory (XOR-swizzled 16-byte chunks, so ldmatrix is bank-conflict free); rows past the
 //     valid length are zero-filled by the copy itself.
 //   * The query heads of the group sit on the M side of mma.sync.m16n8k16 (padded to 16 rows,
@@ -23,7 +23,7 @@ namespace af {
 namespace {
 
 constexpr int DEC_BN = 64;       // keys per pipeline stage
-constexpr int DEC_STAGES = 4;
+constexpr int DEC_STAGES = 3;
 constexpr int DEC_THREADS = 128;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -471,7 +471,7 @@ int launch_decode_static(const AfDecodeParams& in, cudaStream_t st) {
     int dev = 0, sms = 0;
     AF_CUDA_OK(cudaGetDevice(&dev));
     AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    a.num_splits = af_decode_num_splits(a.B, a.H_kv, a.N_kv, sms);
+    a.num_splits = af_decode_num_splits(a.B, a.H_q, a.H_kv, a.N_kv, sms);
   }
   AF_REQUIRE(a.B > 0 && a.H_q > 0 && a.D > 0, "bad sizes");
   const size_t rows = (size_t)a.num_splits * a.B * a.H_q;

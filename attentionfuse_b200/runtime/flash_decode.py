@@ -46,9 +46,9 @@ def _sm_count(device_index: int) -> int:
     return torch.cuda.get_device_properties(device_index).multi_processor_count
 
 
-def _pick_num_splits(B: int, H_kv: int, N_kv: int, device_index: int = 0) -> int:
+def _pick_num_splits(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int = 0) -> int:
     """Split count (stands in for attnfuse/runtime/flash_decode.py:69-95)."""
-    return int(_lib.load().af_decode_num_splits(B, H_kv, N_kv, _sm_count(device_index)))
+    return int(_lib.load().af_decode_num_splits(B, H_q, H_kv, N_kv, _sm_count(device_index)))
 
 
 def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device):
@@ -73,7 +73,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         V = V.contiguous()
     dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     if num_splits is None:
-        num_splits = _pick_num_splits(B, H_kv, N_kv, dev_index)
+        num_splits = _pick_num_splits(B, H_q, H_kv, N_kv, dev_index)
     ws_m, ws_l, ws_acc = workspace if workspace is not None else decode_workspace(
         num_splits, B, H_q, D, Q.device)
 

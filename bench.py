@@ -37,8 +37,9 @@ CFG4 = dict(B=4, H_q=32, H_kv=8, N=4096, D=128, rope_base=500000.0)
 DECODE = dict(B=16, H_q=32, H_kv=8, L=32768, D=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload,
-# from the ncu capture summarised under profiles/ (None until a capture exists).
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = None
+# from the ncu capture summarised under profiles/: the capture ran the same shape at batch 2
+# (traffic grows in proportion to the batch) and is scaled to the batch-4 launch here.
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = 268.4e6   # 134.2 MB captured at batch 2 (profiles/fwd_tcgen05_causal_rope_bf16_d128.md), x2 for batch 4
 
 
 def peaks():
@@ -189,7 +190,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip fwd+bwd / decode side measurements")
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "decode"],
+                    help="run three iterations of a small case of one kernel family and exit (for ncu captures)")
     args = ap.parse_args()
+    if args.profile_case:
+        return profile_case(args.profile_case)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
@@ -311,6 +316,46 @@ def main():
         dist.destroy_process_group()
 
 
+def profile_case(which: str):
+    """Small cases for profiler captures: tensors larger than L2 but only a few hundred MB on the
+    device, three iterations, no timing.  fwd/bwd: the headline shape at batch 2; decode: B8 H32/8
+    D128 L16384 with per-sequence lengths."""
+    import attentionfuse_b200 as af
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode
+    from oracle import attention_oracle as orc
+    dev, dt = torch.device("cuda", 0), torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    @af.attention
+    def causal_rope(Q, K, V):
+        return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+    if which in ("fwd", "bwd"):
+        B, Hq, Hkv, N, D = 2, CFG4["H_q"], CFG4["H_kv"], CFG4["N"], CFG4["D"]
+        grad = which == "bwd"
+        Q = torch.randn(B, Hq, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
+        K = torch.randn(B, Hkv, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
+        V = torch.randn(B, Hkv, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
+        dO = torch.randn(B, Hq, N, D, generator=g, device=dev, dtype=dt)
+        cos, sin = (t.to(dev) for t in orc.build_rope_cache(N, D, CFG4["rope_base"], dt))
+        for _ in range(3):
+            o = causal_rope(Q, K, V, cos=cos, sin=sin)
+            if grad:
+                o.backward(dO)
+                Q.grad = K.grad = V.grad = None
+    else:
+        B, Hq, Hkv, L, D = 8, 32, 8, 16384, 128
+        Q = torch.randn(B, Hq, 1, D, generator=g, device=dev, dtype=dt)
+        K = torch.randn(B, Hkv, L, D, generator=g, device=dev, dtype=dt)
+        V = torch.randn(B, Hkv, L, D, generator=g, device=dev, dtype=dt)
+        lens = torch.randint(L // 2, L + 1, (B,), generator=g, device=dev, dtype=torch.int32)
+        out = torch.empty_like(Q)
+        for _ in range(3):
+            run_flash_decode(None, Q, K, V, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens)
+    torch.cuda.synchronize()
+    print("ok")
+
+
 def bench_decode(dev, rank, world, dist_on, pk):
     """GQA decode at a 32k cache with per-sequence lengths in [L/2, L]: achieved HBM GB/s.
     With more than one rank also the KV-sharded step (local split-K, all-gather, merge)."""
@@ -330,7 +375,7 @@ def bench_decode(dev, rank, world, dist_on, pk):
     Q = torch.randn(B, Hq, 1, D, generator=gen, device=dev, dtype=dt)
     out = torch.empty_like(Q)
     lens_d = lens.to(dev)
-    S = _pick_num_splits(B, Hkv, L, dev.index or 0)
+    S = _pick_num_splits(B, Hq, Hkv, L, dev.index or 0)
     ws = decode_workspace(S, B, Hq, D, dev)
     sm_scale = 1.0 / D ** 0.5
     bytes_step = 2.0 * Hkv * D * 2 * float(lens.sum()) + 2.0 * B * Hq * D * 2

@@ -187,7 +187,7 @@ AF_API int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t 
 
 /* Split count for a decode problem: the reference's _pick_num_splits
  * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  Host only. */
-AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_kv, int32_t N_kv, int32_t sm_count);
+AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count);
 
 /* Which family af_fwd / af_bwd would run for this problem (AF_FAMILY_*), or a negative
  * error.  Host only; stands in for the reference's tile-table lookup
