@@ -83,9 +83,11 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
             from .dispatch import _alibi_slopes
             alibi_slopes = _alibi_slopes(H_q, str(Q.device), str(Q.dtype))
         slopes = alibi_slopes.to(device=Q.device, dtype=Q.dtype).contiguous()
-    if kv_lens is not None:
+    if kv_lens is not None and (kv_lens.device != Q.device or kv_lens.dtype != torch.int32
+                                or not kv_lens.is_contiguous()):
         kv_lens = kv_lens.to(device=Q.device, dtype=torch.int32).contiguous()
-    if q_positions is not None:
+    if q_positions is not None and (q_positions.device != Q.device or q_positions.dtype != torch.int32
+                                    or not q_positions.is_contiguous()):
         q_positions = q_positions.to(device=Q.device, dtype=torch.int32).contiguous()
 
     p = _lib.AfDecodeParams()

@@ -6,7 +6,8 @@ import torch
 import attentionfuse_b200 as af
 from attentionfuse_b200.runtime.dispatch import _alibi_slopes
 from attentionfuse_b200.runtime.flash_decode import run_flash_decode, combine_gathered
-from attentionfuse_b200.runtime.sharded_decode import shard_bounds, sharded_decode
+from attentionfuse_b200.runtime.sharded_decode import (shard_bounds, sharded_decode, ShardedDecodePlan,
+                                                       cyclic_slice, cyclic_local_lengths)
 from oracle import attention_oracle as orc
 from tests._util import assert_close, golden, qkv
 
@@ -105,3 +106,34 @@ def test_kv_sharded_merge_emulated(world):
     assert_close(out, orc.attention(Q, K, V, kv_lens=lens), torch.bfloat16, what=f"sharded world={world}")
     # rank with no valid keys for a row must report LSE = -inf there
     assert torch.isinf(gathered[world - 1, 3, :, D]).all()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("layout", ["contiguous", "cyclic"])
+def test_sharded_plan_layouts_emulated(world, layout):
+    """ShardedDecodePlan on one GPU: each rank's plan runs its local launches, the partials are
+    stacked by hand in place of the all-gather, the merge kernel produces the unsharded result."""
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode as rfd
+    B, Hq, Hkv, L, D = 4, 32, 8, 4096, 128
+    Q, K, V = qkv(995, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+    lens = torch.tensor([4096, 2048, 2049, 300], dtype=torch.int32)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    gathered = torch.empty(world, B, Hq, D + 1, dtype=torch.float32, device=DEV)
+    total_local = torch.zeros(B, dtype=torch.int64)
+    for r in range(world):
+        plan = ShardedDecodePlan(B, Hq, Hkv, D, L, r, world, lens, torch.device(DEV, 0), torch.bfloat16, layout=layout)
+        if layout == "cyclic":
+            kl, vl = cyclic_slice(k, r, world).contiguous(), cyclic_slice(v, r, world).contiguous()
+        else:
+            kl, vl = k[:, :, plan.lo:plan.hi], v[:, :, plan.lo:plan.hi]
+        rfd(None, q, kl, vl, plan.sm_scale, 0, Hkv, None, kv_lens=plan.lens_local, kv_offset=plan.kv_offset,
+            partial=plan.partial, num_splits=plan.num_splits, workspace=plan.workspace)
+        gathered[r].copy_(plan.partial)
+        total_local += plan.lens_local.cpu().long()
+    assert torch.equal(total_local, lens.long())               # every valid key is owned exactly once
+    out = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    combine_gathered(gathered, out)
+    assert_close(out, orc.attention(Q, K, V, kv_lens=lens), torch.bfloat16, what=f"{layout} world={world}")
+    if layout == "cyclic":
+        per_rank = torch.stack([cyclic_local_lengths(lens, r, world) for r in range(world)]).long()
+        assert (per_rank.max(0).values - per_rank.min(0).values).max().item() <= 256   # balanced to one block

@@ -11,7 +11,8 @@ import torch.multiprocessing as mp
 
 import attentionfuse_b200 as af
 from attentionfuse_b200.runtime import partition
-from attentionfuse_b200.runtime.sharded_decode import shard_bounds, local_lengths, sharded_decode, check_gathered
+from attentionfuse_b200.runtime.sharded_decode import (shard_bounds, local_lengths, sharded_decode, check_gathered,
+                                                       cyclic_local_lengths, cyclic_slice)
 from oracle import attention_oracle as orc
 from tests._util import golden
 
@@ -69,6 +70,24 @@ def test_shard_plan():
     assert local_lengths(lens, 16384, 20480).tolist() == [4096, 0, 3616, 0]
     with pytest.raises(ValueError):
         shard_bounds(10, 2, 2)
+
+
+def test_cyclic_layout_is_balanced_and_exact():
+    lens = torch.tensor([32768, 16384, 20000, 5, 0, 2048 + 17])
+    for world in (2, 4, 8):
+        per = torch.stack([cyclic_local_lengths(lens, r, world) for r in range(world)]).long()
+        assert torch.equal(per.sum(0), lens)
+        assert (per.max(0).values - per.min(0).values).max().item() <= 256
+    t = torch.arange(2 * 1 * 2048 * 1).view(2, 1, 2048, 1)
+    parts = [cyclic_slice(t, r, 4) for r in range(4)]
+    assert parts[1][0, 0, :3, 0].tolist() == [256, 257, 258] and parts[1][0, 0, 256, 0].item() == 1024 + 256
+    # the first n local keys of rank r are exactly its keys below the global length
+    L = 1500
+    for r in range(4):
+        n = int(cyclic_local_lengths(torch.tensor([L]), r, 4))
+        assert (parts[r][0, 0, :n, 0] < L).all() and (parts[r][0, 0, n:, 0] >= L).all()
+    with pytest.raises(ValueError):
+        cyclic_slice(t, 0, 3)
 
 
 def _cpu_partial(Q, K, V, sm_scale, bias_kind, lens, kv_offset, q_positions, slopes):
