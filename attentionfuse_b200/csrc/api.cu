@@ -126,6 +126,21 @@ int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t B, int3
   return launch_decode_combine_gathered(gathered, G, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));
 }
 
+int64_t af_decode_exchange_bytes(int32_t world, int32_t B, int32_t H_q, int32_t D) {
+  if (world < 1 || B < 1 || H_q < 1 || D < 1) return 0;
+  return decode_exchange_bytes(world, B, H_q, D);
+}
+
+int af_decode_combine_push(const AfDecodeParams* params, const AfPeerExchange* exchange, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  return launch_decode_combine_push(*params, exchange, static_cast<cudaStream_t>(stream));
+}
+
+int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32_t H_q, int32_t D, int32_t dtype, void* o,
+                         const int64_t o_stride[4], af_stream_t stream) {
+  return launch_decode_wait_merge(exchange, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));
+}
+
 int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count) {
   // One CTA per (split, batch, kv head), two CTAs resident per SM.  Bandwidth-bound groups
   // (<= 16 query heads per KV head) want about five waves of CTAs so that the ragged tail of

@@ -79,7 +79,12 @@ class AfDecodeParams(C.Structure):
     ]
 
 
-EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine", "af_decode_static",
+class AfPeerExchange(C.Structure):
+    _fields_ = [("world", I32), ("rank", I32), ("peer_bases", PTR), ("state", PTR), ("status", PTR),
+                ("wait_cycles", I64)]
+
+
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine", "af_decode_static", "af_decode_exchange_bytes", "af_decode_combine_push", "af_decode_wait_merge",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -110,6 +115,12 @@ def load() -> C.CDLL:
         lib.af_bwd_workspace_bytes.restype = I64
         lib.af_decode_split.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine.argtypes = [C.POINTER(AfDecodeParams), PTR]
+        lib.af_decode_exchange_bytes.argtypes = [I32, I32, I32, I32]
+        lib.af_decode_exchange_bytes.restype = I64
+        lib.af_decode_combine_push.argtypes = [C.POINTER(AfDecodeParams), C.POINTER(AfPeerExchange), PTR]
+        lib.af_decode_combine_push.restype = I32
+        lib.af_decode_wait_merge.argtypes = [C.POINTER(AfPeerExchange), I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
+        lib.af_decode_wait_merge.restype = I32
         lib.af_decode_static.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_static.restype = I32
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]

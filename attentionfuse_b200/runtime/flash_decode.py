@@ -63,7 +63,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      alibi_slopes: Optional[torch.Tensor] = None, kv_offset: int = 0,
                      q_positions: Optional[torch.Tensor] = None,
                      partial: Optional[torch.Tensor] = None,
-                     num_splits: Optional[int] = None, workspace=None) -> torch.Tensor:
+                     num_splits: Optional[int] = None, workspace=None, exchange=None) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
     when only the packed partial is requested)."""
     lib = _lib.load()
@@ -107,6 +107,11 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     with torch.cuda.device(Q.device):
         stream = _lib.current_stream(Q.device)
         _lib.check(lib.af_decode_split(C.byref(p), stream), "af_decode_split")
+        if exchange is not None:
+            # KV-sharded step: the combine pushes this rank's partial to every rank's exchange
+            # buffer; the caller follows up with exchange.wait_merge(out)
+            _lib.check(lib.af_decode_combine_push(C.byref(p), C.byref(exchange.c), stream), "af_decode_combine_push")
+            return None
         _lib.check(lib.af_decode_combine(C.byref(p), stream), "af_decode_combine")
     return out if out is not None else partial
 

@@ -113,6 +113,58 @@ def sharded_decode(Q: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor
     return out
 
 
+class PeerExchange:
+    """One rank's end of the peer-memory exchange of decode partials.
+
+    Multi-process use: the buffer is torch symmetric memory, so every rank can store into every
+    other rank's copy over NVLink.  `peer_buffers` (a list of `world` float32 tensors on ONE
+    device) replaces that for single-GPU tests of the kernels, where the "ranks" are launched
+    one after another."""
+
+    def __init__(self, world: int, rank: int, B: int, H_q: int, D: int, device, *, group=None,
+                 peer_buffers=None, wait_cycles: int = 0):
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        self.world, self.rank, self.B, self.H_q, self.D = world, rank, B, H_q, D
+        n_floats = int(lib.af_decode_exchange_bytes(world, B, H_q, D)) // 4
+        if peer_buffers is None:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buffer = symm_mem.empty(n_floats, dtype=torch.float32, device=device)
+            self.buffer.zero_()
+            torch.cuda.synchronize(device)
+            self._handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in self._handle.buffer_ptrs]
+            dist.barrier(group=group)          # every rank's buffer is zeroed before anyone pushes
+        else:
+            if len(peer_buffers) != world or any(t.numel() < n_floats for t in peer_buffers):
+                raise ValueError("peer_buffers must hold `world` tensors of af_decode_exchange_bytes() bytes")
+            self.buffer = peer_buffers[rank]
+            ptrs = [t.data_ptr() for t in peer_buffers]
+        self.n_floats = n_floats
+        self.peer_bases = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.c = _lib.AfPeerExchange(world, rank, self.peer_bases.data_ptr(), self.state.data_ptr(),
+                                     self.status.data_ptr(), int(wait_cycles))
+
+    def wait_merge(self, out: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        lib = _lib.load()
+        with torch.cuda.device(out.device):
+            rc = lib.af_decode_wait_merge(self.c, self.B, self.H_q, self.D, _lib.dtype_code(out.dtype),
+                                          out.data_ptr(), _lib.strides(out), _lib.current_stream(out.device))
+        _lib.check(rc, "af_decode_wait_merge")
+        return out
+
+    def check_status(self) -> None:
+        """Raise if a bounded wait ran out (synchronises)."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("KV-sharded decode: a peer's partial did not arrive within the wait limit")
+
+
 class ShardedDecodePlan:
     """Everything of a KV-sharded decode step that does not change from token to token, prepared
     once: local valid lengths, ALiBi query positions, split count, workspaces, the packed partial
@@ -122,8 +174,12 @@ class ShardedDecodePlan:
 
     def __init__(self, B: int, H_q: int, H_kv: int, D: int, L_total: int, rank: int, world: int,
                  kv_lens: Optional[torch.Tensor], device, dtype, *, sm_scale: Optional[float] = None,
-                 bias_kind: int = 0, slopes=None, group=None, layout: str = "contiguous"):
+                 bias_kind: int = 0, slopes=None, group=None, layout: str = "contiguous",
+                 exchange: str = "nccl"):
         from .flash_decode import _pick_num_splits, decode_workspace
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError(f"unknown exchange {exchange!r}")
+        self.exchange = None
         self.rank, self.world, self.group = rank, world, group
         self.H_kv, self.bias_kind = H_kv, bias_kind
         self.sm_scale = sm_scale if sm_scale is not None else 1.0 / (D ** 0.5)
@@ -149,10 +205,20 @@ class ShardedDecodePlan:
         self.workspace = decode_workspace(self.num_splits, B, H_q, D, device)
         self.partial = torch.empty(B, H_q, D + 1, dtype=torch.float32, device=device)
         self.gathered = torch.empty(world, B, H_q, D + 1, dtype=torch.float32, device=device)
+        if exchange == "p2p" and world > 1:
+            self.exchange = PeerExchange(world, rank, B, H_q, D, device, group=group)
 
     def step(self, Q: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
         from .flash_decode import run_flash_decode, combine_gathered
+        if self.exchange is not None:
+            # two launches of the local decode (split, combine + push to all peers) and the
+            # wait + merge kernel; no library collective
+            run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, None,
+                             kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
+                             q_positions=self.q_positions, num_splits=self.num_splits,
+                             workspace=self.workspace, exchange=self.exchange)
+            return self.exchange.wait_merge(out)
         run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, None,
                          kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
                          q_positions=self.q_positions, partial=self.partial, num_splits=self.num_splits,

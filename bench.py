@@ -431,6 +431,39 @@ def bench_decode(dev, rank, world, dist_on, pk):
         res["kv_sharded"] = {"world": world, "ms_per_step": mss, "speedup_vs_1gpu_step": ms / mss,
                              "aggregate_gbs": bytes_step / (mss * 1e-3) / 1e9, "local_splits": plan.num_splits, "layout": "cyclic, 256-key blocks",
                              "max_abs_vs_unsharded": err}
+        try:   # fused exchange over peer memory (symmetric memory, no library collective)
+            plan2 = ShardedDecodePlan(B, Hq, Hkv, D, L, rank, world, lens, dev, dt, layout="cyclic", exchange="p2p")
+
+            def sharded_p2p():
+                plan2.step(Q, Kl, Vl, out)
+            for _ in range(5):
+                sharded_p2p()
+            torch.cuda.synchronize()
+            plan2.exchange.check_status()
+            err2 = (out.float() - ref_out.float()).abs().max().item()
+            msp = time_region(sharded_p2p, 30, True) / 30
+            res["kv_sharded_p2p"] = {"world": world, "ms_per_step": msp, "speedup_vs_1gpu_step": ms / msp,
+                                     "max_abs_vs_unsharded": err2, "launches_per_step": 3}
+            gs = torch.cuda.Stream()
+            gs.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(gs):
+                for _ in range(3):
+                    sharded_p2p()
+            torch.cuda.current_stream().wait_stream(gs)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gr3 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr3):
+                for _ in range(10):
+                    sharded_p2p()
+            torch.cuda.synchronize()
+            dist.barrier()
+            msg3 = time_region(gr3.replay, 5, True) / 50
+            plan2.exchange.check_status()
+            res["kv_sharded_p2p"].update({"graph_ms_per_step": msg3, "graph_speedup_vs_1gpu_graph_step":
+                                          res.get("graph_ms_per_step", ms) / msg3})
+        except Exception as e:
+            res["kv_sharded_p2p_error"] = f"{type(e).__name__}: {e}"
         try:   # the same step replayed from a CUDA graph (3 kernels + 1 all-gather per step)
             gs = torch.cuda.Stream()
             gs.wait_stream(torch.cuda.current_stream())

@@ -185,6 +185,36 @@ AF_API int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t 
                                int32_t D, int32_t dtype, void* o, const int64_t o_stride[4],
                                af_stream_t stream);
 
+/* Exchange of per-rank decode partials over peer memory (KV-sharded decode), fused into the
+ * combine kernels instead of a library all-gather between them.  Every rank owns one exchange
+ * buffer of af_decode_exchange_bytes() bytes, zero-initialised once, mapped into every other
+ * rank's address space (e.g. torch symmetric memory); peer_bases[r] is the address of rank r's
+ * buffer as seen from THIS process.  `state` is two zero-initialised uint32 in local device
+ * memory (step counter, CTA counter).  All ranks must make the same sequence of calls.
+ * No counterpart in the reference, which is single-GPU. */
+typedef struct AfPeerExchange {
+  int32_t world, rank;
+  const uint64_t* peer_bases;   /* device array [world]                                      */
+  uint32_t* state;              /* device, local                                             */
+  int32_t*  status;             /* optional device word: AF_STATUS_WAIT_TIMEOUT if a peer's
+                                   partial did not arrive within wait_cycles                */
+  int64_t   wait_cycles;        /* bound of the wait in SM cycles; <= 0: 2^31 (~1 s)          */
+} AfPeerExchange;
+
+AF_API int64_t af_decode_exchange_bytes(int32_t world, int32_t B, int32_t H_q, int32_t D);
+
+/* af_decode_combine + push: merge this rank's splits and store the (normalised O, LSE) rows
+ * into slot `rank` of every rank's exchange buffer, then raise this rank's flag everywhere. */
+AF_API int af_decode_combine_push(const AfDecodeParams* params, const AfPeerExchange* exchange,
+                                  af_stream_t stream);
+
+/* Wait (bounded) for all ranks' flags of the current step, merge the partials from this
+ * rank's own buffer, write o (B, H_q, 1, D).  Call after af_decode_combine_push on the
+ * same stream. */
+AF_API int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32_t H_q, int32_t D,
+                                int32_t dtype, void* o, const int64_t o_stride[4],
+                                af_stream_t stream);
+
 /* Split count for a decode problem: the reference's _pick_num_splits
  * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  Host only. */
 AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count);
