@@ -4,8 +4,8 @@
 //   combine + push   merges this rank's split-K partials (as decode_combine_kernel does) and
 //                    stores the normalised O row and its log-sum-exp straight into slot `rank`
 //                    of EVERY rank's exchange buffer with plain peer stores; the last CTA to
-//                    finish publishes the step number in every rank's flag word (release, system
-//                    scope).
+//                    finish publishes the step number in every rank's flag word (after one
+//                    system-scope fence).
 //   wait + merge     spins (bounded) until all ranks' flags show the current step, then merges
 //                    the `world` partials from its OWN copy of the buffer and writes O.
 //
@@ -22,8 +22,10 @@
 namespace af {
 namespace {
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Flag store.  Ordering against the data comes from ONE system-scope fence issued before the
+// loop over peers; a release store per peer would pay a full system fence each time.
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -86,18 +88,19 @@ __global__ void decode_combine_push_kernel(const AfDecodeParams a, const AfPeerE
       if (lane == 0) base[lay.lse_off(parity, x.rank, rows) + row] = lse;
     }
   }
-  // Publish: every thread's peer stores are fenced, the CTA counts itself in, and the last CTA
-  // advances the local step and raises this rank's flag on every peer.
-  __threadfence_system();
+  // Publish: the CTA barrier orders every thread's peer stores before thread 0, whose system-scope
+  // fence then makes them visible before it counts the CTA in; the last CTA advances the local
+  // step and raises this rank's flag on every peer.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const uint32_t done = atomicAdd(&x.state[1], 1u);
     if (done == gridDim.x - 1) {
       x.state[1] = 0;
       __threadfence_system();
       for (int peer = 0; peer < x.world; ++peer) {
         uint32_t* flags = reinterpret_cast<uint32_t*>(reinterpret_cast<float*>(x.peer_bases[peer]) + lay.flag_off_floats());
-        st_release_sys(flags + parity * x.world + x.rank, step);
+        st_relaxed_sys(flags + parity * x.world + x.rank, step);
       }
       x.state[0] = step;
       __threadfence();
@@ -135,19 +138,28 @@ __global__ void decode_wait_merge_kernel(const AfPeerExchange x, int rows, int H
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
+  // all log-sum-exps first (independent loads), then the weighted rows
+  float w[32];
   float mstar = -INFINITY;
-  for (int r = 0; r < x.world; ++r) mstar = fmaxf(mstar, base[lay.lse_off(parity, r, rows) + row]);
+#pragma unroll 8
+  for (int r = 0; r < x.world; ++r) {
+    w[r & 31] = base[lay.lse_off(parity, r, rows) + row];
+    mstar = fmaxf(mstar, w[r & 31]);
+  }
   const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
   float wsum = 0.f;
-  for (int r = 0; r < x.world; ++r) wsum += expf(base[lay.lse_off(parity, r, rows) + row] - m_use);
+#pragma unroll 8
+  for (int r = 0; r < x.world; ++r) {
+    w[r & 31] = (w[r & 31] == -INFINITY) ? 0.f : expf(w[r & 31] - m_use);
+    wsum += w[r & 31];
+  }
   const float inv = (mstar == -INFINITY) ? 0.f : 1.f / wsum;
   T* dst = o + (int64_t)(row / H_q) * s0 + (int64_t)(row % H_q) * s1;
   for (int d = lane; d < D; d += 32) {
     float acc = 0.f;
-    for (int r = 0; r < x.world; ++r) {
-      const float lse = base[lay.lse_off(parity, r, rows) + row];
-      if (lse != -INFINITY) acc += expf(lse - m_use) * base[lay.o_off(parity, r, rows, D) + (int64_t)row * D + d];
-    }
+#pragma unroll 8
+    for (int r = 0; r < x.world; ++r)
+      if (w[r & 31] != 0.f) acc += w[r & 31] * base[lay.o_off(parity, r, rows, D) + (int64_t)row * D + d];
     dst[(int64_t)d * s3] = Elem<T>::from_f32(acc * inv);
   }
 }
