@@ -21,6 +21,8 @@
 // S^T/dP^T (or S/dP) are double-buffered in TMEM so the MMA warp computes step i+1 while the
 // 128 element-wise threads work on step i.  All waits are bounded.
 #pragma once
+#include <type_traits>
+
 #include "fwd_tcgen05.cuh"
 
 namespace af {
@@ -314,28 +316,46 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         const int rel = srow - r0;   // DKV: query c kept iff c >= rel;  DQ: key c kept iff c <= rel
 
         uint32_t pk[BT / 2], dk[BT / 2];
+        const float relf = (float)rel;
+        // The masking decision is taken once per tile: the element loop exists in a masked and an
+        // unmasked copy, and the per-column statistics come in float4 shared-memory loads.
+        auto element_pass = [&](auto masked_tag) {
+          constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-        for (int c = 0; c < BT; c += 2) {
-          float pe[2], de[2];
+          for (int c = 0; c < BT; c += 4) {
+            float l2v[4], dlv[4];
+            if (MODE == MODE_DKV) {
+              const float4 a4 = *reinterpret_cast<const float4*>(stats + c);
+              const float4 b4 = *reinterpret_cast<const float4*>(stats + BT + c);
+              l2v[0] = a4.x; l2v[1] = a4.y; l2v[2] = a4.z; l2v[3] = a4.w;
+              dlv[0] = b4.x; dlv[1] = b4.y; dlv[2] = b4.z; dlv[3] = b4.w;
+            } else {
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cc = c + u;
-            const float l2 = (MODE == MODE_DKV) ? stats[cc] : l2_row;
-            const float dl = (MODE == MODE_DKV) ? stats[BT + cc] : dl_row;
-            float e = fmaf(__uint_as_float(xr[cc]), scale2, -l2);
-            if (ALIBI) e -= slope2 * fabsf((float)rel - (float)cc);
-            float pr = ex2_approx(e);
-            if (need_mask) {
-              bool keep = cc < col_limit;
-              if (EMASK == EMASK_CAUSAL) keep = keep && ((MODE == MODE_DKV) ? (cc >= rel) : (cc <= rel));
-              pr = keep ? pr : 0.f;
+              for (int u = 0; u < 4; ++u) { l2v[u] = l2_row; dlv[u] = dl_row; }
             }
-            pe[u] = pr;
-            de[u] = pr * (__uint_as_float(yr[cc]) - dl);
+            float pe[4], de[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int cc = c + u;
+              float e = fmaf(__uint_as_float(xr[cc]), scale2, -l2v[u]);
+              if (ALIBI) e -= slope2 * fabsf(relf - (float)cc);
+              float pr = ex2_approx(e);
+              if (MASKED) {
+                bool keep = cc < col_limit;
+                if (EMASK == EMASK_CAUSAL) keep = keep && ((MODE == MODE_DKV) ? (cc >= rel) : (cc <= rel));
+                pr = keep ? pr : 0.f;
+              }
+              pe[u] = pr;
+              de[u] = pr * (__uint_as_float(yr[cc]) - dlv[u]);
+            }
+            pk[c >> 1] = Pack2<T>::run(pe[0], pe[1]);
+            pk[(c >> 1) + 1] = Pack2<T>::run(pe[2], pe[3]);
+            dk[c >> 1] = Pack2<T>::run(de[0], de[1]);
+            dk[(c >> 1) + 1] = Pack2<T>::run(de[2], de[3]);
           }
-          pk[c >> 1] = Pack2<T>::run(pe[0], pe[1]);
-          dk[c >> 1] = Pack2<T>::run(de[0], de[1]);
-        }
+        };
+        if (need_mask) element_pass(std::true_type{});
+        else element_pass(std::false_type{});
         if (MODE == MODE_DKV) tmem_st32(xt, pk);
         tmem_st32(yt, dk);
         tmem_wait_st();
