@@ -44,7 +44,7 @@ template <int D> struct BCfg {
   static constexpr int STRM_PANEL = BT * 128;
   static constexpr int STAT_TILE = PANELS * STAT_PANEL;
   static constexpr int STRM_TILE = PANELS * STRM_PANEL;
-  static constexpr int STAGES = 3;
+  static constexpr int STAGES = 4;
   static constexpr int STATS_BYTES = 2 * BT * 4;            // L*log2e and delta of a streamed tile
   static constexpr int SMEM_BYTES = 2 * STAT_TILE + STAGES * (2 * STRM_TILE + STATS_BYTES) + 1024 + 512;
   static constexpr int TMEM_COLS = 512;
@@ -195,6 +195,16 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
           if (it >= STAGES && !mbar_wait(&bars->strm_empty[st], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
           const int r0 = w.row0(s);
           unsigned char* stage = smem + 2 * C::STAT_TILE + st * STAGE_BYTES;
+          // The TMA loads go out first; the statistics of the streamed rows (two global loads per
+          // lane) are fetched while they fly, and the warp's arrival completes the stage.
+          if (lane == 0) {
+            mbar_expect_tx(&bars->strm_full[st], 2 * C::STRM_TILE);
+#pragma unroll
+            for (int pn = 0; pn < C::PANELS; ++pn) {
+              tma_load_4d(stage + pn * C::STRM_PANEL, &map_b1, &bars->strm_full[st], pn * 64, r0, hb, b);
+              tma_load_4d(stage + C::STRM_TILE + pn * C::STRM_PANEL, &map_b2, &bars->strm_full[st], pn * 64, r0, hb, b);
+            }
+          }
           if (MODE == MODE_DKV) {
             // L*log2e and delta of the 64 streamed query rows; rows past N_q get (+inf, 0) so that
             // their probabilities are exactly zero.
@@ -213,20 +223,16 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
             }
             __syncwarp();
           }
-          if (lane == 0) {
-            mbar_arrive_expect_tx(&bars->strm_full[st], 2 * C::STRM_TILE);
-#pragma unroll
-            for (int pn = 0; pn < C::PANELS; ++pn) {
-              tma_load_4d(stage + pn * C::STRM_PANEL, &map_b1, &bars->strm_full[st], pn * 64, r0, hb, b);
-              tma_load_4d(stage + C::STRM_TILE + pn * C::STRM_PANEL, &map_b2, &bars->strm_full[st], pn * 64, r0, hb, b);
-            }
-          }
+          if (lane == 0) mbar_arrive(&bars->strm_full[st]);
         }
       }
     }
   } else if (warp == 5) {
     // ============================== MMA issuer ==============================
     if (lane == 0 && total_steps > 0) {
+      const uint64_t desc_a1 = umma_desc_sw128(sA1, 16, 1024), desc_a2 = umma_desc_sw128(sA2, 16, 1024);
+      const uint64_t desc_b1k = umma_desc_sw128(sStage0, 16, 1024);              // streamed tile, K-major
+      const uint64_t desc_b1n = umma_desc_sw128(sStage0, C::STRM_PANEL, 1024);   // streamed tile, N-major
       bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
       tc_fence_after_sync();
       auto issue_xy = [&](int it) -> bool {
@@ -234,16 +240,17 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) return false;
         if (it >= 2 && !mbar_wait(&bars->acc_done[t], ((it >> 1) - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
-        const uint32_t b1 = sStage0 + st * STAGE_BYTES, b2 = b1 + C::STRM_TILE;
+        // Descriptors are built once; k-steps and ring stages only move the start-address field.
+        const uint64_t b1 = desc_b1k + (uint64_t)((st * STAGE_BYTES) >> 4), b2 = b1 + (uint64_t)(C::STRM_TILE >> 4);
         const uint32_t xt = tmem + (t ? C::COL_X1 : C::COL_X0), yt = tmem + (t ? C::COL_Y1 : C::COL_Y0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss(xt, umma_desc_sw128(sA1 + (kk >> 2) * C::STAT_PANEL + (kk & 3) * 32, 16, 1024),
-                  umma_desc_sw128(b1 + (kk >> 2) * C::STRM_PANEL + (kk & 3) * 32, 16, 1024), IDESC_XY, kk > 0 ? 1u : 0u);
+          umma_ss(xt, desc_a1 + (uint64_t)(((kk >> 2) * C::STAT_PANEL + (kk & 3) * 32) >> 4),
+                  b1 + (uint64_t)(((kk >> 2) * C::STRM_PANEL + (kk & 3) * 32) >> 4), IDESC_XY, kk > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          umma_ss(yt, umma_desc_sw128(sA2 + (kk >> 2) * C::STAT_PANEL + (kk & 3) * 32, 16, 1024),
-                  umma_desc_sw128(b2 + (kk >> 2) * C::STRM_PANEL + (kk & 3) * 32, 16, 1024), IDESC_XY, kk > 0 ? 1u : 0u);
+          umma_ss(yt, desc_a2 + (uint64_t)(((kk >> 2) * C::STAT_PANEL + (kk & 3) * 32) >> 4),
+                  b2 + (uint64_t)(((kk >> 2) * C::STRM_PANEL + (kk & 3) * 32) >> 4), IDESC_XY, kk > 0 ? 1u : 0u);
         umma_commit(&bars->xy_full[t]);
         return true;
       };
@@ -254,22 +261,22 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         const int st = it % STAGES, t = it & 1;
         if (!mbar_wait(&bars->p_full[t], (it >> 1) & 1, abort_flag)) break;
         tc_fence_after_sync();
-        const uint32_t b1 = sStage0 + st * STAGE_BYTES, b2 = b1 + C::STRM_TILE;
+        const uint64_t b1 = desc_b1n + (uint64_t)((st * STAGE_BYTES) >> 4), b2 = b1 + (uint64_t)(C::STRM_TILE >> 4);
         const uint32_t xt = tmem + (t ? C::COL_X1 : C::COL_X0), yt = tmem + (t ? C::COL_Y1 : C::COL_Y0);
         // streamed tiles as N-major B operands: 16 rows per k-step (2048 B), panels LBO apart
         if (MODE == MODE_DKV) {
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dV += P^T dO
-            umma_ts(tmem + C::COL_ACC1, xt + kk * 8, umma_desc_sw128(b2 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+            umma_ts(tmem + C::COL_ACC1, xt + kk * 8, b2 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
                     (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dK += dS^T Q
-            umma_ts(tmem + C::COL_ACC2, yt + kk * 8, umma_desc_sw128(b1 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+            umma_ts(tmem + C::COL_ACC2, yt + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
                     (it > 0 || kk > 0) ? 1u : 0u);
         } else {
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dQ += dS K
-            umma_ts(tmem + C::COL_ACC1, yt + kk * 8, umma_desc_sw128(b1 + kk * 2048, C::STRM_PANEL, 1024), IDESC_ACC,
+            umma_ts(tmem + C::COL_ACC1, yt + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
                     (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars->strm_empty[st]);

@@ -273,6 +273,9 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   } else if (warp == 5) {
     // ============================== MMA issuer ==============================
     if (lane == 0 && n_tiles > 0) {
+      const uint64_t desc_q0 = umma_desc_sw128(sQ, 16, 1024);
+      const uint64_t desc_k0 = umma_desc_sw128(sK0, 16, 1024);
+      const uint64_t desc_v0 = umma_desc_sw128(sV0, PANEL_BYTES, 1024);
       bool ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, 0, abort_flag);
       tc_fence_after_sync();
       auto issue_qk = [&](int j) -> bool {
@@ -281,12 +284,13 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (j >= 2 && !mbar_wait(&bars->pv_done[t], ((j >> 1) - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
-        const uint32_t kbase = sK0 + s * C::TILE_BYTES;
+        // Descriptors are built once; a k-step or a ring stage only moves the start-address
+        // field (address >> 4), so the single issuing thread spends one add per operand.
+        const uint64_t kdesc = desc_k0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * PANEL_BYTES + (kk & 3) * 32;
-          umma_ss(d_tmem, umma_desc_sw128(sQ + off, 16, 1024), umma_desc_sw128(kbase + off, 16, 1024), IDESC_QK,
-                  kk > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
+          umma_ss(d_tmem, desc_q0 + off, kdesc + off, IDESC_QK, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->k_empty[s]);
         umma_commit(&bars->s_full[t]);
@@ -301,12 +305,12 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (!mbar_wait(&bars->p_full[t], (j >> 1) & 1, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
-        const uint32_t vbase = sV0 + s * C::TILE_BYTES;
+        const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns of
-          // D live one panel further (LBO).
-          umma_ts(tmem + C::COL_O, p_tmem + kk * 8, umma_desc_sw128(vbase + kk * 2048, PANEL_BYTES, 1024), IDESC_PV,
+          // D live one panel further (LBO).  16 keys further = 2048 bytes.
+          umma_ts(tmem + C::COL_O, p_tmem + kk * 8, vdesc + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
                   (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars->v_empty[s]);
