@@ -1,7 +1,6 @@
 """Generate the golden fixtures in this directory from the REFERENCE project's own code.
 
-Run in a container that has the reference checkout (default /root/reference, override with
-$ATTNFUSE_REF):
+Run on a machine that has a checkout of the reference project; point $ATTNFUSE_REF at it:
 
     python tests/golden/make_golden.py
 
@@ -24,7 +23,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("ATTNFUSE_REF", "/root/reference"))
+REF = Path(os.environ.get("ATTNFUSE_REF", Path.home() / "reference"))
 
 
 def load_reference():
