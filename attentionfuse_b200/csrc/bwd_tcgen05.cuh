@@ -49,6 +49,9 @@ template <int D> struct BCfg {
   static constexpr int SMEM_BYTES = 2 * STAT_TILE + STAGES * (2 * STRM_TILE + STATS_BYTES) + 1024 + 512;
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_X0 = 0, COL_Y0 = 64, COL_X1 = 128, COL_Y1 = 192, COL_ACC1 = 256, COL_ACC2 = 256 + D;
+  // MODE_DQ has one accumulator only: dS gets columns of its own (two buffers of 32), so the next
+  // S / dP product does not have to wait until dQ += dS K has consumed the previous dS.
+  static constexpr int COL_DS0 = 384, COL_DS1 = 416;
 };
 
 struct BBarriers {
@@ -238,7 +241,10 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
       auto issue_xy = [&](int it) -> bool {
         const int st = it % STAGES, t = it & 1;
         if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) return false;
-        if (it >= 2 && !mbar_wait(&bars->acc_done[t], ((it >> 1) - 1) & 1, abort_flag)) return false;
+        // X/Y[t] were last read by the element-wise group for step it-2, which this thread has
+        // already waited for; only MODE_DKV, whose P^T / dS^T overwrite X/Y, must also wait for the
+        // accumulate MMAs of that step.
+        if (MODE == MODE_DKV && it >= 2 && !mbar_wait(&bars->acc_done[t], ((it >> 1) - 1) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         // Descriptors are built once; k-steps and ring stages only move the start-address field.
         const uint64_t b1 = desc_b1k + (uint64_t)((st * STAGE_BYTES) >> 4), b2 = b1 + (uint64_t)(C::STRM_TILE >> 4);
@@ -274,9 +280,10 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
             umma_ts(tmem + C::COL_ACC2, yt + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
                     (it > 0 || kk > 0) ? 1u : 0u);
         } else {
+          const uint32_t dst = tmem + (t ? C::COL_DS1 : C::COL_DS0);
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dQ += dS K
-            umma_ts(tmem + C::COL_ACC1, yt + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
+            umma_ts(tmem + C::COL_ACC1, dst + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
                     (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars->strm_empty[st]);
@@ -363,8 +370,14 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         };
         if (need_mask) element_pass(std::true_type{});
         else element_pass(std::false_type{});
-        if (MODE == MODE_DKV) tmem_st32(xt, pk);
-        tmem_st32(yt, dk);
+        if (MODE == MODE_DKV) {
+          tmem_st32(xt, pk);
+          tmem_st32(yt, dk);
+        } else {
+          // dS buffer t was last read by the accumulate MMAs of step it-2
+          if (it >= 2 && !mbar_wait(&bars->acc_done[t], ((it >> 1) - 1) & 1, abort_flag)) { alive = false; break; }
+          tmem_st32(tmem + lane_base + (t ? C::COL_DS1 : C::COL_DS0), dk);
+        }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&bars->p_full[t]);
