@@ -4,7 +4,10 @@
 // block-sparse sibling (attnfuse/compiler/codegen_blocksparse.py:34-171) for f16/bf16 inputs
 // with head_dim 64 or 128 and softmax normalisation.
 //
-// One CTA owns 128 query rows of one (batch, query head) and walks 128-key tiles:
+// A work item is 128 query rows of one (batch, query head) against its 128-key tiles.  The kernel
+// is persistent: one CTA per SM takes items in a zig-zag over the heaviest-first item list, and
+// the barrier phases run on per-CTA running counts, so the loads and the first S product of the
+// next item are under way while the previous item's output is still being written.  Roles:
 //
 //   producer warp   TMA loads: the Q tile once, then K and V tiles into a STAGES-deep ring of
 //                   128-byte-swizzled shared-memory tiles (no cluster multicast anywhere).
@@ -53,10 +56,11 @@ template <int D> struct Cfg {
 };
 
 struct Barriers {
-  uint64_t q_full, q_ready;
+  uint64_t q_full, q_ready, q_empty;
   uint64_t k_full[4], k_ready[4], k_empty[4];
   uint64_t v_full[4], v_empty[4];
   uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t o_free;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -66,6 +70,8 @@ struct TcArgs {
   int num_m_blocks;
   int kv_tiles_per_block;   // block_n / 128 for block lists
   int q_tiles_per_block;    // block_m / 128
+  int total_items;          // num_m_blocks * B * H_q query tiles
+  int grid_ctas;            // CTAs to launch: one per SM (persistent) or one per item
 };
 
 // Which key tiles a query tile visits.
@@ -104,6 +110,34 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   }
   if (w.n_tiles < 0) w.n_tiles = 0;
   return w;
+}
+
+// One work item = one 128-row query tile of one (batch, query head).
+struct Item {
+  int m0, b, h, h_kv;
+  TileWalk walk;
+};
+
+// Items are numbered heaviest first (causal: the last query tiles).  A CTA takes item
+// r*G + c in even rounds r and r*G + (G-1-c) in odd rounds (c = blockIdx.x, G = gridDim.x): with
+// item weights that fall monotonically the zig-zag evens out the key tiles per CTA to within a
+// fraction of a percent.  With G = number of items every CTA runs exactly one item.
+template <int EMASK>
+__device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const int64_t w64 = (int64_t)round * G + ((round & 1) ? G - 1 - c : c);
+  if (w64 >= args.total_items) return false;
+  const int w = (int)w64;
+  const AfProblem& p = args.a.p;
+  const int bh_count = p.B * p.H_q;
+  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - w / bh_count) : (w / bh_count);
+  const int bh = w % bh_count;
+  it.b = bh / p.H_q;
+  it.h = bh % p.H_q;
+  it.h_kv = it.h / (p.H_q / p.H_kv);
+  it.m0 = m_blk * BM;
+  it.walk = make_walk(p, args, m_blk, it.h);
+  return true;
 }
 
 template <typename T> struct Pack2;
@@ -204,20 +238,16 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  // Tile assignment: the heaviest query tiles (causal: the last ones) are issued first.
-  const int bh_count = p.B * p.H_q;
-  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - (int)(blockIdx.x / bh_count))
-                                            : (int)(blockIdx.x / bh_count);
-  const int bh = blockIdx.x % bh_count;
-  const int b = bh / p.H_q, h = bh % p.H_q;
-  const int h_kv = h / (p.H_q / p.H_kv);
-  const int m0 = m_blk * BM;
-  const TileWalk walk = make_walk(p, args, m_blk, h);
-  const int n_tiles = walk.n_tiles;
-
+  // Every role walks the same item sequence (get_item) and keeps two running counts: `g`, key
+  // tiles processed so far by this CTA (ring stage g % STAGES, S buffer g & 1, barrier phases
+  // derived from g), and `qi`, items with at least one key tile (phases of the Q / O hand-overs).
+  // The pipeline therefore runs across item boundaries: the first S product of the next item is
+  // issued while the softmax group still writes the previous item's output.
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
     mbar_init(&bars->q_ready, 128);
+    mbar_init(&bars->q_empty, 1);
+    mbar_init(&bars->o_free, 128);
     for (int s = 0; s < 4; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_ready[s], 64);
@@ -244,40 +274,51 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 
   if (warp == 4) {
     // ============================== TMA producer ==============================
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
-#pragma unroll
-      for (int pn = 0; pn < C::PANELS; ++pn)
-        tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, m0, h, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % STAGES;
-        const uint32_t par = ((j / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
-        const int key0 = walk.key0(j);
-        unsigned char* dk = smem + C::TILE_BYTES * (1 + s);
-        unsigned char* dv = smem + C::TILE_BYTES * (1 + STAGES + s);
-        if (j >= STAGES && !mbar_wait(&bars->k_empty[s], par, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+      Item it;
+      int g = 0, qi = 0;
+      bool ok = true;
+      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+        const int n_tiles = it.walk.n_tiles;
+        if (n_tiles == 0) continue;
+        // the single Q buffer is free once the last S product of the previous item has run
+        if (qi > 0 && !mbar_wait(&bars->q_empty, (qi - 1) & 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
 #pragma unroll
         for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, h_kv, b);
-        if (j >= STAGES && !mbar_wait(&bars->v_empty[s], par, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+          tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, it.m0, it.h, it.b);
+        for (int j = 0; j < n_tiles; ++j) {
+          const int gg = g + j;
+          const int s = gg % STAGES;
+          const uint32_t par = ((gg / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
+          const int key0 = it.walk.key0(j);
+          unsigned char* dk = smem + C::TILE_BYTES * (1 + s);
+          unsigned char* dv = smem + C::TILE_BYTES * (1 + STAGES + s);
+          if (gg >= STAGES && !mbar_wait(&bars->k_empty[s], par, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars->k_full[s], C::TILE_BYTES);
 #pragma unroll
-        for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, h_kv, b);
+          for (int pn = 0; pn < C::PANELS; ++pn)
+            tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, it.h_kv, it.b);
+          if (gg >= STAGES && !mbar_wait(&bars->v_empty[s], par, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+#pragma unroll
+          for (int pn = 0; pn < C::PANELS; ++pn)
+            tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, it.h_kv, it.b);
+        }
+        g += n_tiles;
+        ++qi;
       }
     }
   } else if (warp == 5) {
     // ============================== MMA issuer ==============================
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
       const uint64_t desc_q0 = umma_desc_sw128(sQ, 16, 1024);
       const uint64_t desc_k0 = umma_desc_sw128(sK0, 16, 1024);
       const uint64_t desc_v0 = umma_desc_sw128(sV0, PANEL_BYTES, 1024);
-      bool ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, 0, abort_flag);
-      tc_fence_after_sync();
+      // S product of the CTA's key tile number j (running count over all items)
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES, t = j & 1;
         if (!mbar_wait(ROT_K ? &bars->k_ready[s] : &bars->k_full[s], (j / STAGES) & 1, abort_flag)) return false;
@@ -296,187 +337,227 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         umma_commit(&bars->s_full[t]);
         return true;
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+      Item it;
+      int g = 0, qi = 0;
+      bool ok = true;
+      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+        const int n_tiles = it.walk.n_tiles;
+        if (n_tiles == 0) continue;
+        ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, qi & 1, abort_flag);
         if (!ok) break;
-        const int s = j % STAGES, t = j & 1;
-        if (!mbar_wait(&bars->v_full[s], (j / STAGES) & 1, abort_flag)) break;
-        if (!mbar_wait(&bars->p_full[t], (j >> 1) & 1, abort_flag)) break;
         tc_fence_after_sync();
-        const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
-        const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
+        ok = issue_qk(g);
+        if (ok && n_tiles == 1) umma_commit(&bars->q_empty);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          const int gg = g + j;
+          if (j + 1 < n_tiles) {
+            ok = issue_qk(gg + 1);
+            // the item's last S product: the Q buffer may be refilled when it has run
+            if (ok && j + 2 == n_tiles) umma_commit(&bars->q_empty);
+          }
+          if (!ok) break;
+          const int s = gg % STAGES, t = gg & 1;
+          if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&bars->p_full[t], (gg >> 1) & 1, abort_flag)) { ok = false; break; }
+          // the first P.V product of an item overwrites O: the previous item's rows must be read out
+          if (j == 0 && qi > 0 && !mbar_wait(&bars->o_free, (qi - 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
+          const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns of
-          // D live one panel further (LBO).  16 keys further = 2048 bytes.
-          umma_ts(tmem + C::COL_O, p_tmem + kk * 8, vdesc + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
-                  (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns of
+            // D live one panel further (LBO).  16 keys further = 2048 bytes.
+            umma_ts(tmem + C::COL_O, p_tmem + kk * 8, vdesc + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->v_empty[s]);
+          umma_commit(&bars->pv_done[t]);
         }
-        umma_commit(&bars->v_empty[s]);
-        umma_commit(&bars->pv_done[t]);
+        g += n_tiles;
+        ++qi;
       }
     }
   } else if (warp < 4) {
     // ============================== softmax / epilogue ==============================
-    const int row = m0 + tid;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    if (ROPE != ROPE_NONE && n_tiles > 0) {
-      if (mbar_wait(&bars->q_full, 0, abort_flag)) {
-        if (row < p.N_q)
-          rope_row<T, D>(sQ, tid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
-                         reinterpret_cast<const T*>(p.sin) + (int64_t)row * p.rope_stride_n);
-        fence_proxy_async_smem();
-        mbar_arrive(&bars->q_ready);
-      }
-    }
     const float scale2 = p.sm_scale * kLog2e;     // > 0 (checked on the host)
-    const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
-    float m_ref = -INFINITY, l_sum = 0.f;         // m_ref in log2 units of the scaled score
+    Item it;
+    int g = 0, qi = 0;
     bool alive = true;
-
-    for (int j = 0; j < n_tiles; ++j) {
-      const int t = j & 1;
-      const int key0 = walk.key0(j);
-      if (!mbar_wait(&bars->s_full[t], (j >> 1) & 1, abort_flag)) { alive = false; break; }
-      tc_fence_after_sync();
-      const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
-      uint32_t xr[BN];   // fp32 bit patterns of this row's raw scores
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, &xr[c * 32]);
-      tmem_wait_ld();
-
-      // Tile-level decision: only edge / diagonal tiles pay for element masking.
-      bool need_mask = key0 + BN > p.N_kv;
-      if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
-      if (EMASK == EMASK_WINDOW)
-        need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
-      const int rel = row - key0;                 // key index c is kept iff ...
-      if (need_mask) {
-        const int kmax = p.N_kv - key0;           // ... c < kmax
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          bool keep = c < kmax;
-          if (EMASK == EMASK_CAUSAL) keep = keep && (c <= rel);
-          if (EMASK == EMASK_WINDOW) keep = keep && (c - rel < p.window) && (rel - c < p.window);
-          xr[c] = keep ? xr[c] : 0xff800000u;     // -inf
+    for (int round = 0; alive && get_item<EMASK>(args, round, it); ++round) {
+      const TileWalk& walk = it.walk;
+      const int n_tiles = walk.n_tiles;
+      const int m0 = it.m0, b = it.b, h = it.h;
+      const int row = m0 + tid;
+      if (ROPE != ROPE_NONE && n_tiles > 0) {
+        if (mbar_wait(&bars->q_full, qi & 1, abort_flag)) {
+          if (row < p.N_q)
+            rope_row<T, D>(sQ, tid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
+                           reinterpret_cast<const T*>(p.sin) + (int64_t)row * p.rope_stride_n);
+          fence_proxy_async_smem();
+          mbar_arrive(&bars->q_ready);
         }
       }
-      if (ALIBI) {
-        const float relf = (float)rel;
-#pragma unroll
-        for (int c = 0; c < BN; ++c)
-          xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < BN; c += 4) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
-      const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
-      const float m_next = bump ? mx : m_ref;
-      const float alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
-      m_ref = m_next;
-      const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
+      const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
+      float m_ref = -INFINITY, l_sum = 0.f;         // m_ref in log2 units of the scaled score
 
-      if (j > 0 && __any_sync(0xffffffffu, bump)) {
-        // The accumulator is expressed relative to the old reference: rescale it in TMEM once
-        // the previous P.V product has landed.
-        if (!mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int gg = g + j;                       // the CTA's running key-tile count
+        const int t = gg & 1;
+        const int key0 = walk.key0(j);
+        if (!mbar_wait(&bars->s_full[t], (gg >> 1) & 1, abort_flag)) { alive = false; break; }
         tc_fence_after_sync();
+        const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
+        uint32_t xr[BN];   // fp32 bit patterns of this row's raw scores
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
-        }
-        tmem_wait_st();
-      }
+        for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, &xr[c * 32]);
+        tmem_wait_ld();
 
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[BN / 2];
+        // Tile-level decision: only edge / diagonal tiles pay for element masking.
+        bool need_mask = key0 + BN > p.N_kv;
+        if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
+        if (EMASK == EMASK_WINDOW)
+          need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
+        const int rel = row - key0;                 // key index c is kept iff ...
+        if (need_mask) {
+          const int kmax = p.N_kv - key0;           // ... c < kmax
 #pragma unroll
-      for (int c = 0; c < BN; c += 4) {
-        float e[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float x = __uint_as_float(xr[c + u]);
-          e[u] = ex2_approx(ALIBI ? x + neg_m : fmaf(x, scale2, neg_m));
-          rs4[u] += e[u];
-        }
-        pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
-        pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
-      }
-      l_sum = l_sum * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
-      tmem_st32(s_tmem, &pk[0]);
-      tmem_st32(s_tmem + 32, &pk[32]);
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&bars->p_full[t]);
-    }
-
-    // Epilogue: O / l, store row; L = m + log(l).
-    if (alive && n_tiles > 0) {
-      const int jl = n_tiles - 1;
-      alive = mbar_wait(&bars->pv_done[jl & 1], (jl >> 1) & 1, abort_flag);
-      tc_fence_after_sync();
-    }
-    if (alive) {
-      const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
-      const float inv = 1.f / safe_l;
-      T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +
-                (int64_t)row * a.o_stride[2];
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (row < p.N_q) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 v;
-            v.x = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
-            v.y = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
-            v.z = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
-            v.w = Pack2<T>::run(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = v;
+          for (int c = 0; c < BN; ++c) {
+            bool keep = c < kmax;
+            if (EMASK == EMASK_CAUSAL) keep = keep && (c <= rel);
+            if (EMASK == EMASK_WINDOW) keep = keep && (c - rel < p.window) && (rel - c < p.window);
+            xr[c] = keep ? xr[c] : 0xff800000u;     // -inf
           }
         }
+        if (ALIBI) {
+          const float relf = (float)rel;
+#pragma unroll
+          for (int c = 0; c < BN; ++c)
+            xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < BN; c += 4) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
+        const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
+        const float m_next = bump ? mx : m_ref;
+        const float alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
+        m_ref = m_next;
+        const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
+
+        if (j > 0 && __any_sync(0xffffffffu, bump)) {
+          // The accumulator is expressed relative to the old reference: rescale it in TMEM once
+          // the previous P.V product has landed.
+          if (!mbar_wait(&bars->pv_done[(gg - 1) & 1], ((gg - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[BN / 2];
+#pragma unroll
+        for (int c = 0; c < BN; c += 4) {
+          float e[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float x = __uint_as_float(xr[c + u]);
+            e[u] = ex2_approx(ALIBI ? x + neg_m : fmaf(x, scale2, neg_m));
+            rs4[u] += e[u];
+          }
+          pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
+          pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
+        }
+        l_sum = l_sum * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+        tmem_st32(s_tmem, &pk[0]);
+        tmem_st32(s_tmem + 32, &pk[32]);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&bars->p_full[t]);
       }
-      if (a.lse != nullptr && row < p.N_q)
-        a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
-            m_ref * kLn2 + logf(safe_l);
+
+      // Epilogue: read the row of O out of TMEM, hand the accumulator back to the MMA warp, then
+      // O / l -> global; L = m + log(l).
+      if (!alive) break;
+      uint32_t o[D];
+      if (n_tiles > 0) {
+        const int gl = g + n_tiles - 1;
+        if (!mbar_wait(&bars->pv_done[gl & 1], (gl >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld32(tmem + lane_base + C::COL_O + c * 32, &o[c * 32]);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(&bars->o_free);
+      } else {
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0u;
+      }
+      {
+        const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
+        const float inv = 1.f / safe_l;
+        T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +
+                  (int64_t)row * a.o_stride[2];
+        if (row < p.N_q) {
+#pragma unroll
+          for (int q8 = 0; q8 < D / 8; ++q8) {
+            uint4 v;
+            v.x = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 0]) * inv, __uint_as_float(o[q8 * 8 + 1]) * inv);
+            v.y = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 2]) * inv, __uint_as_float(o[q8 * 8 + 3]) * inv);
+            v.z = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 4]) * inv, __uint_as_float(o[q8 * 8 + 5]) * inv);
+            v.w = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 6]) * inv, __uint_as_float(o[q8 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + q8 * 8) = v;
+          }
+          if (a.lse != nullptr)
+            a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
+                m_ref * kLn2 + logf(safe_l);
+        }
+      }
+      if (n_tiles > 0) {
+        g += n_tiles;
+        ++qi;
+      }
     }
   } else if (ROT_K && warp >= 6) {
     // ============================== K rotation group ==============================
     // Two warps (eight warps per CTA keep 255 registers per thread available to the softmax
     // group); each thread rotates two key rows of the tile.
     const int r0 = tid - 192;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j % STAGES;
-      if (!mbar_wait(&bars->k_full[s], (j / STAGES) & 1, abort_flag)) break;
-      const int key0 = walk.key0(j);
+    Item it;
+    int g = 0;
+    bool ok = true;
+    for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+      const int n_tiles = it.walk.n_tiles;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int gg = g + j;
+        const int s = gg % STAGES;
+        if (!mbar_wait(&bars->k_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
+        const int key0 = it.walk.key0(j);
 #pragma unroll 1
-      for (int r = r0; r < BN; r += 64) {
-        const int pos = key0 + r;
-        if (pos < p.N_kv)
-          rope_row<T, D>(sK0 + s * C::TILE_BYTES, r,
-                         reinterpret_cast<const T*>(p.cos) + (int64_t)pos * p.rope_stride_n,
-                         reinterpret_cast<const T*>(p.sin) + (int64_t)pos * p.rope_stride_n);
+        for (int r = r0; r < BN; r += 64) {
+          const int pos = key0 + r;
+          if (pos < p.N_kv)
+            rope_row<T, D>(sK0 + s * C::TILE_BYTES, r,
+                           reinterpret_cast<const T*>(p.cos) + (int64_t)pos * p.rope_stride_n,
+                           reinterpret_cast<const T*>(p.sin) + (int64_t)pos * p.rope_stride_n);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars->k_ready[s]);
       }
-      fence_proxy_async_smem();
-      mbar_arrive(&bars->k_ready[s]);
+      g += n_tiles;
     }
   }
 
@@ -503,9 +584,7 @@ int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  const AfProblem& p = args.a.p;
-  const int64_t ctas = (int64_t)args.num_m_blocks * p.B * p.H_q;
-  kern<<<(unsigned)ctas, ROPE == ROPE_FUSED ? 256 : 192, smem, st>>>(args, mq, mk, mv);
+  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 256 : 192, smem, st>>>(args, mq, mk, mv);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
 }
