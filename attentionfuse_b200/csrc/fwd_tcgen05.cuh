@@ -22,8 +22,9 @@
 //                   no shuffles): tcgen05.ld the S row, apply scale, ALiBi, causal / window /
 //                   length masks, online softmax in base 2, write P as f16/bf16 over the S
 //                   buffer with tcgen05.st.  O stays in TMEM; it is rescaled only when a row max
-//                   grew by more than 2^8 since the value the accumulator is expressed in
-//                   (the result is mathematically unchanged: P, l and O share that reference).
+//                   grew by more than 2^6 since the value the accumulator is expressed in
+//                   (the result is mathematically unchanged: P, l and O share that reference),
+//                   and in the steady state no separate pass for the tile maximum runs at all.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status word, drains and
 // frees its TMEM.
@@ -44,7 +45,13 @@ enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };  // element-level m
 constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;   // 128 rows x 64 elements x 2 bytes
-constexpr float kRescaleThreshold = 8.f; // log2 units
+// The reference maximum of a row moves only when a tile maximum exceeds it by more than
+// kRescaleThreshold (log2 units).  A tile processed without looking at its maximum first is accepted
+// when its row sum stays below kRowSumBound: every term is then below the bound too, far inside the
+// f16 range, and a rejected tile has a term above kRowSumBound / 128 = 2^kRescaleThreshold, so the
+// classic pass that follows is certain to move the reference and the next tile is accepted again.
+constexpr float kRescaleThreshold = 6.f;
+constexpr float kRowSumBound = 8192.f;   // 128 * 2^kRescaleThreshold
 
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
@@ -208,6 +215,38 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Row maximum of 128 fp32 bit patterns, four independent chains.
+__device__ __forceinline__ float row_max(const uint32_t (&xr)[BN]) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < BN; c += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
+  }
+  return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+}
+
+// P = 2^(x * scale2 + neg_m) (ALiBi rows are already scaled: 2^(x + neg_m)) packed to T, and the
+// row sum of the unrounded values.
+template <typename T, bool PRESCALED>
+__device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk)[BN / 2], float scale2, float neg_m,
+                                         float& rsum) {
+  float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < BN; c += 4) {
+    float e[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float x = __uint_as_float(xr[c + u]);
+      e[u] = ex2_approx(PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m));
+      rs4[u] += e[u];
+    }
+    pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
+    pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
+  }
+  rsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
 }
 
 // One instantiation per composition: element type, head_dim, RoPE mode, element-level mask and
@@ -436,52 +475,46 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           for (int c = 0; c < BN; ++c)
             xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int c = 0; c < BN; c += 4) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
-        }
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
-        const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
-        const float m_next = bump ? mx : m_ref;
-        const float alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
-        m_ref = m_next;
-        const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
-
-        if (j > 0 && __any_sync(0xffffffffu, bump)) {
-          // The accumulator is expressed relative to the old reference: rescale it in TMEM once
-          // the previous P.V product has landed.
-          if (!mbar_wait(&bars->pv_done[(gg - 1) & 1], ((gg - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
-          tc_fence_after_sync();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
-          }
-          tmem_wait_st();
-        }
-
-        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        // Usual case: the row already has a reference maximum and this tile does not exceed it by
+        // much.  Then P is formed against the standing reference right away, without a pass for
+        // the tile maximum; the row sum verifies the assumption for free (all terms are
+        // non-negative, an overflow gives +inf; see kRowSumBound).  Otherwise -- first tile of an
+        // item, a row with no visible key so far, or a sum past the bound -- the classic order
+        // runs: maximum first, reference update, accumulator rescale, then P.
+        float alpha = 1.f, rsum = 0.f;
         uint32_t pk[BN / 2];
-#pragma unroll
-        for (int c = 0; c < BN; c += 4) {
-          float e[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const float x = __uint_as_float(xr[c + u]);
-            e[u] = ex2_approx(ALIBI ? x + neg_m : fmaf(x, scale2, neg_m));
-            rs4[u] += e[u];
-          }
-          pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
-          pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
+        bool fast = j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY);
+        if (fast) {
+          exp_pass<T, ALIBI>(xr, pk, scale2, -m_ref, rsum);
+          fast = !__any_sync(0xffffffffu, !(rsum <= kRowSumBound));
         }
-        l_sum = l_sum * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
+        if (!fast) {
+          float mx = row_max(xr);
+          if (!ALIBI) mx *= scale2;
+          const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
+          const float m_next = bump ? mx : m_ref;
+          alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
+          m_ref = m_next;
+          const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
+          if (j > 0 && __any_sync(0xffffffffu, bump)) {
+            // The accumulator is expressed relative to the old reference: rescale it in TMEM once
+            // the previous P.V product has landed.
+            if (!mbar_wait(&bars->pv_done[(gg - 1) & 1], ((gg - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+          exp_pass<T, ALIBI>(xr, pk, scale2, neg_m, rsum);
+        }
+        l_sum = l_sum * alpha + rsum;
         tmem_st32(s_tmem, &pk[0]);
         tmem_st32(s_tmem + 32, &pk[32]);
         tmem_wait_st();

@@ -251,3 +251,29 @@ def test_rope_prepass_and_in_kernel_rotation_agree(D, dtype, monkeypatch):
     assert_close(pre, want, dtype, what="pre-pass")
     assert_close(fused, want, dtype, what="in-kernel")
     assert torch.equal(pre, fused)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("variant", ["dense", "causal", "causal_alibi"])
+def test_row_maximum_jumps_in_late_tiles(variant, dtype):
+    """The softmax group forms P against the standing reference maximum and only verifies the
+    tile maximum on the side; a tile that raises the maximum by more than the rescale threshold
+    must fall back to the classic order (and rescale the accumulator).  Keys grow along the
+    sequence, and a few rows see one very large key late."""
+    B, Hq, Hkv, N, D = 1, 4, 2, 700, 128
+    Q, K, V = qkv(1200, B, Hq, Hkv, N, N, D, dtype)
+    ramp = torch.linspace(0.2, 6.0, N).view(1, 1, N, 1)
+    K = (K.float() * ramp).to(dtype)
+    K[:, :, 650] = (K[:, :, 650].float() * 3).to(dtype)
+    got, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05)
+    assert_close(got, want, dtype, what=f"late maxima {variant} {dtype}")
+
+
+@pytest.mark.parametrize("variant", ["dense", "causal", "window", "causal_rope"])
+def test_more_items_than_sms(variant):
+    """One CTA per SM walks several query tiles: phases of the Q / O hand-over and of the K/V
+    ring carry across items, including items of different lengths (causal, window)."""
+    B, Hq, Hkv, N, D = 3, 16, 4, 1100, 64     # 3*16*9 = 432 query tiles
+    Q, K, V = qkv(1300, B, Hq, Hkv, N, N, D, torch.bfloat16)
+    got, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05, window=200)
+    assert_close(got, want, torch.bfloat16, what=f"persistent {variant}")
