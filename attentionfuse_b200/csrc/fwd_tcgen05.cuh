@@ -11,13 +11,14 @@
 //
 //   producer warp   TMA loads: the Q tile once, then K and V tiles into a STAGES-deep ring of
 //                   128-byte-swizzled shared-memory tiles (no cluster multicast anywhere).
-//   rotation group  (RoPE only) two warps rotate each K tile in place in shared memory as it
+//   rotation warp   (RoPE only) one warp rotates each K tile in place in shared memory as it
 //                   lands -- fp32 math, rounded back to the input dtype exactly as the reference
 //                   does before its dot (codegen.py:332-341) -- then hand it to the MMA warp.
 //                   The Q tile is rotated once by the softmax group (codegen.py:126-135).
-//   MMA warp        one thread issues  S = Q K^T  (tcgen05.mma, operands from shared memory,
-//                   fp32 accumulator in TMEM, two S buffers) and  O += P V  (P read from TMEM,
-//                   V from shared memory, N-major), and commits to mbarriers.
+//   MMA warps       one thread issues  S = Q K^T  (tcgen05.mma, operands from shared memory,
+//                   fp32 accumulator in TMEM, two S buffers), a thread of another warp issues
+//                   O += P V  (P read from TMEM, V from shared memory, N-major); both commit to
+//                   mbarriers.
 //   softmax group   128 threads, one query row each (TMEM lane = row, so row max / row sum need
 //                   no shuffles): tcgen05.ld the S row, apply scale, ALiBi, causal / window /
 //                   length masks, online softmax in base 2, write P as f16/bf16 over the S
@@ -253,7 +254,7 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk
 // ALiBi are compile-time, so the per-element code of the softmax group carries no run-time
 // branches on the composition.
 template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
-__global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 256 : 192, 1)
+__global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 256 : 224, 1)
 fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
   using C = Cfg<D>;
@@ -289,7 +290,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     mbar_init(&bars->o_free, 128);
     for (int s = 0; s < 4; ++s) {
       mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->k_ready[s], 64);
+      mbar_init(&bars->k_ready[s], 32);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
@@ -352,30 +353,13 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       }
     }
   } else if (warp == 5) {
-    // ============================== MMA issuer ==============================
+    // ============================== MMA issuer 1: S = Q K^T ==============================
+    // The two products are issued by two threads.  A tcgen05.mma issue blocks while the pipe's
+    // short queue is full, so a single issuing thread leaves the pipe idle during its own barrier
+    // waits and commits (measured: about 800 of 2000 cycles per key tile).
     if (lane == 0) {
       const uint64_t desc_q0 = umma_desc_sw128(sQ, 16, 1024);
       const uint64_t desc_k0 = umma_desc_sw128(sK0, 16, 1024);
-      const uint64_t desc_v0 = umma_desc_sw128(sV0, PANEL_BYTES, 1024);
-      // S product of the CTA's key tile number j (running count over all items)
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % STAGES, t = j & 1;
-        if (!mbar_wait(ROT_K ? &bars->k_ready[s] : &bars->k_full[s], (j / STAGES) & 1, abort_flag)) return false;
-        if (j >= 2 && !mbar_wait(&bars->pv_done[t], ((j >> 1) - 1) & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
-        // Descriptors are built once; a k-step or a ring stage only moves the start-address
-        // field (address >> 4), so the single issuing thread spends one add per operand.
-        const uint64_t kdesc = desc_k0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
-          umma_ss(d_tmem, desc_q0 + off, kdesc + off, IDESC_QK, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->k_empty[s]);
-        umma_commit(&bars->s_full[t]);
-        return true;
-      };
       Item it;
       int g = 0, qi = 0;
       bool ok = true;
@@ -383,23 +367,48 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         const int n_tiles = it.walk.n_tiles;
         if (n_tiles == 0) continue;
         ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, qi & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        ok = issue_qk(g);
-        if (ok && n_tiles == 1) umma_commit(&bars->q_empty);
         for (int j = 0; ok && j < n_tiles; ++j) {
-          const int gg = g + j;
-          if (j + 1 < n_tiles) {
-            ok = issue_qk(gg + 1);
-            // the item's last S product: the Q buffer may be refilled when it has run
-            if (ok && j + 2 == n_tiles) umma_commit(&bars->q_empty);
+          const int gg = g + j;                       // the CTA's running key-tile count
+          const int s = gg % STAGES, t = gg & 1;
+          if (!mbar_wait(ROT_K ? &bars->k_ready[s] : &bars->k_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
+          // S buffer t still holds P of tile gg-2 until its P.V product has run
+          if (gg >= 2 && !mbar_wait(&bars->pv_done[t], ((gg >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
+          // Descriptors are built once; a k-step or a ring stage only moves the start-address
+          // field (address >> 4), so the issuing thread spends one add per operand.
+          const uint64_t kdesc = desc_k0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
+            umma_ss(d_tmem, desc_q0 + off, kdesc + off, IDESC_QK, kk > 0 ? 1u : 0u);
           }
-          if (!ok) break;
+          umma_commit(&bars->k_empty[s]);
+          umma_commit(&bars->s_full[t]);
+          // the item's last S product: the Q buffer may be refilled when it has run
+          if (j + 1 == n_tiles) umma_commit(&bars->q_empty);
+        }
+        g += n_tiles;
+        ++qi;
+      }
+    }
+  } else if (warp == 6) {
+    // ============================== MMA issuer 2: O += P V ==============================
+    if (lane == 0) {
+      const uint64_t desc_v0 = umma_desc_sw128(sV0, PANEL_BYTES, 1024);
+      Item it;
+      int g = 0, qi = 0;
+      bool ok = true;
+      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+        const int n_tiles = it.walk.n_tiles;
+        if (n_tiles == 0) continue;
+        for (int j = 0; j < n_tiles; ++j) {
+          const int gg = g + j;
           const int s = gg % STAGES, t = gg & 1;
           if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(&bars->p_full[t], (gg >> 1) & 1, abort_flag)) { ok = false; break; }
           // the first P.V product of an item overwrites O: the previous item's rows must be read out
           if (j == 0 && qi > 0 && !mbar_wait(&bars->o_free, (qi - 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&bars->p_full[t], (gg >> 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
           const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
@@ -564,11 +573,11 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         ++qi;
       }
     }
-  } else if (ROT_K && warp >= 6) {
-    // ============================== K rotation group ==============================
-    // Two warps (eight warps per CTA keep 255 registers per thread available to the softmax
-    // group); each thread rotates two key rows of the tile.
-    const int r0 = tid - 192;
+  } else if (ROT_K && warp == 7) {
+    // ============================== K rotation warp ==============================
+    // One warp (eight warps per CTA keep 255 registers per thread available to the softmax
+    // group); each thread rotates four key rows of the tile.
+    const int r0 = tid - 224;
     Item it;
     int g = 0;
     bool ok = true;
@@ -580,7 +589,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (!mbar_wait(&bars->k_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
         const int key0 = it.walk.key0(j);
 #pragma unroll 1
-        for (int r = r0; r < BN; r += 64) {
+        for (int r = r0; r < BN; r += 32) {
           const int pos = key0 + r;
           if (pos < p.N_kv)
             rope_row<T, D>(sK0 + s * C::TILE_BYTES, r,
@@ -617,7 +626,7 @@ int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 256 : 192, smem, st>>>(args, mq, mk, mv);
+  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 256 : 224, smem, st>>>(args, mq, mk, mv);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
 }
