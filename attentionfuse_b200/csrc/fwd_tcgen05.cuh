@@ -53,6 +53,10 @@ constexpr int PANEL_BYTES = 128 * 128;   // 128 rows x 64 elements x 2 bytes
 // classic pass that follows is certain to move the reference and the next tile is accepted again.
 constexpr float kRescaleThreshold = 6.f;
 constexpr float kRowSumBound = 8192.f;   // 128 * 2^kRescaleThreshold
+#ifndef AF_POLY_PER_EIGHT
+#define AF_POLY_PER_EIGHT 0
+#endif
+constexpr int kPolyPerEight = AF_POLY_PER_EIGHT;   // exponentials per 8 columns evaluated on the FMA pipe
 
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
@@ -229,9 +233,24 @@ __device__ __forceinline__ float row_max(const uint32_t (&xr)[BN]) {
   return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 }
 
+// 2^x on the FMA pipe: round-to-nearest split x = n + f with the 1.5 * 2^23 trick (n lands in the
+// low mantissa bits), a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5, well below the f16 /
+// bf16 rounding of P) and n added to the exponent field.  Inputs below -125 give 2^-125.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float r = x + 12582912.f;
+  const float f = x - (r - 12582912.f);
+  float p = fmaf(0.05517151f, f, 0.24261098f);
+  p = fmaf(p, f, 0.69326097f);
+  p = fmaf(p, f, 0.99992806f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
 // P = 2^(x * scale2 + neg_m) (ALiBi rows are already scaled: 2^(x + neg_m)) packed to T, and the
-// row sum of the unrounded values.
-template <typename T, bool PRESCALED>
+// row sum of the unrounded values.  The exponentials are MUFU-bound (16 per clock per SM, as many
+// cycles per tile as the tile's MMAs), so POLY of every 8 columns are evaluated on the FMA pipe
+// instead; POLY = 0 keeps all of them on the MUFU (tiles with masked, -inf, entries).
+template <typename T, bool PRESCALED, int POLY>
 __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk)[BN / 2], float scale2, float neg_m,
                                          float& rsum) {
   float rs4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -240,8 +259,10 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk
     float e[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const float x = __uint_as_float(xr[c + u]);
-      e[u] = ex2_approx(PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m));
+      const int cc = c + u;
+      const float x = __uint_as_float(xr[cc]);
+      const float y = PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m);
+      e[u] = ((cc * POLY) % 8 < POLY) ? ex2_poly(y) : ex2_approx(y);
       rs4[u] += e[u];
     }
     pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
@@ -494,7 +515,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         uint32_t pk[BN / 2];
         bool fast = j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY);
         if (fast) {
-          exp_pass<T, ALIBI>(xr, pk, scale2, -m_ref, rsum);
+          if (need_mask) exp_pass<T, ALIBI, 0>(xr, pk, scale2, -m_ref, rsum);
+          else exp_pass<T, ALIBI, kPolyPerEight>(xr, pk, scale2, -m_ref, rsum);
           fast = !__any_sync(0xffffffffu, !(rsum <= kRowSumBound));
         }
         if (!fast) {
@@ -521,7 +543,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
             }
             tmem_wait_st();
           }
-          exp_pass<T, ALIBI>(xr, pk, scale2, neg_m, rsum);
+          exp_pass<T, ALIBI, 0>(xr, pk, scale2, neg_m, rsum);
         }
         l_sum = l_sum * alpha + rsum;
         tmem_st32(s_tmem, &pk[0]);
