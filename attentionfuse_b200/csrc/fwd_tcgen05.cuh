@@ -19,13 +19,17 @@
 //                   fp32 accumulator in TMEM, two S buffers), a thread of another warp issues
 //                   O += P V  (P read from TMEM, V from shared memory, N-major); both commit to
 //                   mbarriers.
-//   softmax group   128 threads, one query row each (TMEM lane = row, so row max / row sum need
-//                   no shuffles): tcgen05.ld the S row, apply scale, ALiBi, causal / window /
-//                   length masks, online softmax in base 2, write P as f16/bf16 over the S
-//                   buffer with tcgen05.st.  O stays in TMEM; it is rescaled only when a row max
-//                   grew by more than 2^6 since the value the accumulator is expressed in
-//                   (the result is mathematically unchanged: P, l and O share that reference),
-//                   and in the steady state no separate pass for the tile maximum runs at all.
+//   softmax group   256 threads, two per query row (TMEM lane = row, so row max / row sum need
+//                   no shuffles); each thread owns 64 of a tile's 128 key columns and runs an
+//                   online softmax of its own over them -- own reference maximum, own row sum,
+//                   own accumulator O_h in TMEM -- so the two warps that share a scheduler never
+//                   synchronise inside the tile loop.  Per tile: tcgen05.ld the S columns, apply
+//                   scale, ALiBi, causal / window / length masks, exponentials in base 2, write
+//                   P as f16/bf16 over the thread's own S columns with tcgen05.st.  O_h is
+//                   rescaled only when the maximum grew by more than 2^6 since the value the
+//                   accumulator is expressed in (the result is mathematically unchanged: P, l and
+//                   O share that reference), and in the steady state no separate pass for the tile
+//                   maximum runs at all.  The two halves of a row are merged once per item.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises a status word, drains and
 // frees its TMEM.
@@ -53,28 +57,32 @@ constexpr int PANEL_BYTES = 128 * 128;   // 128 rows x 64 elements x 2 bytes
 // classic pass that follows is certain to move the reference and the next tile is accepted again.
 constexpr float kRescaleThreshold = 6.f;
 constexpr float kRowSumBound = 8192.f;   // 128 * 2^kRescaleThreshold
-#ifndef AF_POLY_PER_EIGHT
-#define AF_POLY_PER_EIGHT 0
-#endif
-constexpr int kPolyPerEight = AF_POLY_PER_EIGHT;   // exponentials per 8 columns evaluated on the FMA pipe
 
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
   static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;     // one Q, K or V tile
   static constexpr int STAGES = (D == 128) ? 3 : 4;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 /*align*/ + 1536 /*barriers, exchange*/;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + D;   // one O per half of the key columns
 };
+
+// Warp roles.  The softmax group has two threads per query row: warps 0-3 take key columns
+// 0..63 of a tile, warps 4-7 columns 64..127 (warp w and w+4 own the same 32 TMEM lanes).
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int HALF_COLS = BN / 2;
+enum { WARP_PRODUCER = 8, WARP_QK = 9, WARP_PV = 10, WARP_ROTATE = 11 };
 
 struct Barriers {
   uint64_t q_full, q_ready, q_empty;
   uint64_t k_full[4], k_ready[4], k_empty[4];
   uint64_t v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2][2], pv_done[2];   // p_full[S buffer][half]
   uint64_t o_free;
   uint32_t tmem_base;
   int abort_flag;
+  uint32_t pair_flag[2][8];   // hand-shake counts of the softmax warps, two slots by parity of the count
+  float xchg[SOFTMAX_THREADS];   // reference maximum / row sum exchange between the two halves of a row
 };
 
 struct TcArgs {
@@ -222,47 +230,64 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// Row maximum of 128 fp32 bit patterns, four independent chains.
-__device__ __forceinline__ float row_max(const uint32_t (&xr)[BN]) {
+// Hand-shake between the two warps that share 32 query rows (warp w and w ^ 4).  Each warp
+// publishes its hand-shake count with a release store and polls the partner's word with acquire
+// loads; whatever both wrote to shared memory before is visible afterwards.  The words alternate
+// between two slots by the parity of the count, so a warp that runs ahead to its next hand-shake
+// cannot overwrite a word its partner has not read yet.  The wait is bounded like the mbarrier
+// waits (a hardware named barrier would hang if the partner left after a time-out).
+__device__ __forceinline__ bool pair_sync(Barriers* bars, int warp, int lane, uint32_t& count,
+                                          volatile int* abort_flag) {
+  ++count;
+  tc_fence_before_sync();   // orders this thread's TMEM accesses against the partner's
+  __syncwarp();
+  uint32_t* mine = &bars->pair_flag[count & 1][warp];
+  const uint32_t* theirs = &bars->pair_flag[count & 1][warp ^ 4];
+  if (lane == 0)
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(mine)), "r"(count) : "memory");
+  const long long t0 = clock64();
+  uint32_t v, spins = 0;
+  for (;;) {
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(theirs)) : "memory");
+    if (v == count) break;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_after_sync();
+  return true;
+}
+
+// Maximum of NC fp32 bit patterns, four independent chains.
+template <int NC>
+__device__ __forceinline__ float row_max(const uint32_t (&xr)[NC]) {
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-  for (int c = 0; c < BN; c += 4) {
+  for (int c = 0; c < NC; c += 4) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(xr[c + u]));
   }
   return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 }
 
-// 2^x on the FMA pipe: round-to-nearest split x = n + f with the 1.5 * 2^23 trick (n lands in the
-// low mantissa bits), a cubic for 2^f on [-0.5, 0.5] (relative error 7.5e-5, well below the f16 /
-// bf16 rounding of P) and n added to the exponent field.  Inputs below -125 give 2^-125.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float r = x + 12582912.f;
-  const float f = x - (r - 12582912.f);
-  float p = fmaf(0.05517151f, f, 0.24261098f);
-  p = fmaf(p, f, 0.69326097f);
-  p = fmaf(p, f, 0.99992806f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
-}
-
 // P = 2^(x * scale2 + neg_m) (ALiBi rows are already scaled: 2^(x + neg_m)) packed to T, and the
-// row sum of the unrounded values.  The exponentials are MUFU-bound (16 per clock per SM, as many
-// cycles per tile as the tile's MMAs), so POLY of every 8 columns are evaluated on the FMA pipe
-// instead; POLY = 0 keeps all of them on the MUFU (tiles with masked, -inf, entries).
-template <typename T, bool PRESCALED, int POLY>
-__device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk)[BN / 2], float scale2, float neg_m,
+// row sum of the unrounded values.
+template <typename T, bool PRESCALED, int NC>
+__device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk)[NC / 2], float scale2, float neg_m,
                                          float& rsum) {
   float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int c = 0; c < BN; c += 4) {
+  for (int c = 0; c < NC; c += 4) {
     float e[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int cc = c + u;
-      const float x = __uint_as_float(xr[cc]);
-      const float y = PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m);
-      e[u] = ((cc * POLY) % 8 < POLY) ? ex2_poly(y) : ex2_approx(y);
+      const float x = __uint_as_float(xr[c + u]);
+      e[u] = ex2_approx(PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m));
       rs4[u] += e[u];
     }
     pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
@@ -275,7 +300,7 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[BN], uint32_t (&pk
 // ALiBi are compile-time, so the per-element code of the softmax group carries no run-time
 // branches on the composition.
 template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
-__global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 256 : 224, 1)
+__global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 384 : 352, 1)
 fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
   using C = Cfg<D>;
@@ -308,7 +333,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     mbar_init(&bars->q_full, 1);
     mbar_init(&bars->q_ready, 128);
     mbar_init(&bars->q_empty, 1);
-    mbar_init(&bars->o_free, 128);
+    mbar_init(&bars->o_free, SOFTMAX_THREADS);
     for (int s = 0; s < 4; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_ready[s], 32);
@@ -318,13 +343,15 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->p_full[t][0], SOFTMAX_THREADS / 2);
+      mbar_init(&bars->p_full[t][1], SOFTMAX_THREADS / 2);
       mbar_init(&bars->pv_done[t], 1);
     }
     bars->abort_flag = 0;
+    for (int i = 0; i < 16; ++i) (&bars->pair_flag[0][0])[i] = 0u;
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == WARP_PRODUCER) {
     tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -333,7 +360,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == WARP_PRODUCER) {
     // ============================== TMA producer ==============================
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
@@ -373,7 +400,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         ++qi;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_QK) {
     // ============================== MMA issuer 1: S = Q K^T ==============================
     // The two products are issued by two threads.  A tcgen05.mma issue blocks while the pipe's
     // short queue is full, so a single issuing thread leaves the pipe idle during its own barrier
@@ -413,7 +440,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         ++qi;
       }
     }
-  } else if (warp == 6) {
+  } else if (warp == WARP_PV) {
     // ============================== MMA issuer 2: O += P V ==============================
     if (lane == 0) {
       const uint64_t desc_v0 = umma_desc_sw128(sV0, PANEL_BYTES, 1024);
@@ -429,17 +456,24 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
           // the first P.V product of an item overwrites O: the previous item's rows must be read out
           if (j == 0 && qi > 0 && !mbar_wait(&bars->o_free, (qi - 1) & 1, abort_flag)) { ok = false; break; }
-          if (!mbar_wait(&bars->p_full[t], (gg >> 1) & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
           const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
+          // The halves of the key columns are independent softmax streams with accumulators of
+          // their own: O_h += P_h V[64h .. 64h+64), issued as soon as that half's P is there.
+          // P_h sits in the first 32 columns of the half's own 64 S columns.
+          for (int hh = 0; hh < 2 && ok; ++hh) {
+            if (!mbar_wait(&bars->p_full[t][hh], (gg >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t p_tmem = tmem + (t ? C::COL_S1 : C::COL_S0) + hh * HALF_COLS;
+            const uint32_t o_tmem = tmem + (hh ? C::COL_O1 : C::COL_O0);
 #pragma unroll
-          for (int kk = 0; kk < BN / 16; ++kk) {
-            // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns of
-            // D live one panel further (LBO).  16 keys further = 2048 bytes.
-            umma_ts(tmem + C::COL_O, p_tmem + kk * 8, vdesc + (uint64_t)((kk * 2048) >> 4), IDESC_PV,
-                    (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < HALF_COLS / 16; ++kk) {
+              // V tile is N-major: 16 keys = two 8-row groups (SBO 1024 B); the second 64 columns
+              // of D live one panel further (LBO).  16 keys further = 2048 bytes.
+              umma_ts(o_tmem, p_tmem + kk * 8, vdesc + (uint64_t)(((hh * 4 + kk) * 2048) >> 4), IDESC_PV,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+            }
           }
+          if (!ok) break;
           umma_commit(&bars->v_empty[s]);
           umma_commit(&bars->pv_done[t]);
         }
@@ -447,29 +481,37 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         ++qi;
       }
     }
-  } else if (warp < 4) {
+  } else if (warp < SOFTMAX_THREADS / 32) {
     // ============================== softmax / epilogue ==============================
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // Two threads per query row: this thread owns row `rtid` of the item and the key columns
+    // [half * 64, half * 64 + 64) of every tile.  The two halves are independent online-softmax
+    // streams over disjoint key sets -- own reference maximum, own row sum, own accumulator O_h in
+    // TMEM -- that never synchronise inside the tile loop, so the two warps of a scheduler drift
+    // out of phase and one warp's exponentials (MUFU) overlap the other's loads, stores and waits.
+    // They are merged once per item in the epilogue.
+    const int half = warp >> 2, rtid = tid & (BM - 1);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;     // > 0 (checked on the host)
     Item it;
     int g = 0, qi = 0;
+    uint32_t pair_count = 0;
     bool alive = true;
     for (int round = 0; alive && get_item<EMASK>(args, round, it); ++round) {
       const TileWalk& walk = it.walk;
       const int n_tiles = walk.n_tiles;
       const int m0 = it.m0, b = it.b, h = it.h;
-      const int row = m0 + tid;
-      if (ROPE != ROPE_NONE && n_tiles > 0) {
+      const int row = m0 + rtid;
+      if (ROPE != ROPE_NONE && n_tiles > 0 && half == 0) {
         if (mbar_wait(&bars->q_full, qi & 1, abort_flag)) {
           if (row < p.N_q)
-            rope_row<T, D>(sQ, tid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
+            rope_row<T, D>(sQ, rtid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
                            reinterpret_cast<const T*>(p.sin) + (int64_t)row * p.rope_stride_n);
           fence_proxy_async_smem();
           mbar_arrive(&bars->q_ready);
         }
       }
       const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
-      float m_ref = -INFINITY, l_sum = 0.f;         // m_ref in log2 units of the scaled score
+      float m_ref = -INFINITY, l_part = 0.f;        // m_ref in log2 units of the scaled score
 
       for (int j = 0; j < n_tiles; ++j) {
         const int gg = g + j;                       // the CTA's running key-tile count
@@ -478,9 +520,10 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (!mbar_wait(&bars->s_full[t], (gg >> 1) & 1, abort_flag)) { alive = false; break; }
         tc_fence_after_sync();
         const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
-        uint32_t xr[BN];   // fp32 bit patterns of this row's raw scores
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(s_tmem + c * 32, &xr[c * 32]);
+        const uint32_t o_tmem = tmem + lane_base + (half ? C::COL_O1 : C::COL_O0);
+        uint32_t xr[HALF_COLS];   // fp32 bit patterns of this thread's raw scores
+        tmem_ld32(s_tmem + half * HALF_COLS, &xr[0]);
+        tmem_ld32(s_tmem + half * HALF_COLS + 32, &xr[32]);
         tmem_wait_ld();
 
         // Tile-level decision: only edge / diagonal tiles pay for element masking.
@@ -488,11 +531,12 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
         if (EMASK == EMASK_WINDOW)
           need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
-        const int rel = row - key0;                 // key index c is kept iff ...
+        const int col0 = key0 + half * HALF_COLS;   // key index of this thread's column 0
+        const int rel = row - col0;                 // column c is kept iff ...
         if (need_mask) {
-          const int kmax = p.N_kv - key0;           // ... c < kmax
+          const int kmax = p.N_kv - col0;           // ... c < kmax
 #pragma unroll
-          for (int c = 0; c < BN; ++c) {
+          for (int c = 0; c < HALF_COLS; ++c) {
             bool keep = c < kmax;
             if (EMASK == EMASK_CAUSAL) keep = keep && (c <= rel);
             if (EMASK == EMASK_WINDOW) keep = keep && (c - rel < p.window) && (rel - c < p.window);
@@ -502,26 +546,25 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (ALIBI) {
           const float relf = (float)rel;
 #pragma unroll
-          for (int c = 0; c < BN; ++c)
+          for (int c = 0; c < HALF_COLS; ++c)
             xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
         }
-        // Usual case: the row already has a reference maximum and this tile does not exceed it by
-        // much.  Then P is formed against the standing reference right away, without a pass for
-        // the tile maximum; the row sum verifies the assumption for free (all terms are
+        // Usual case: this half of the row already has a reference maximum and the tile does not
+        // exceed it by much.  Then P is formed against the standing reference right away, without
+        // a pass for the tile maximum; the row sum verifies the assumption for free (all terms are
         // non-negative, an overflow gives +inf; see kRowSumBound).  Otherwise -- first tile of an
-        // item, a row with no visible key so far, or a sum past the bound -- the classic order
-        // runs: maximum first, reference update, accumulator rescale, then P.
+        // item, no visible key so far, or a sum past the bound -- the classic order runs: maximum
+        // first, reference update, accumulator rescale, then P.
         float alpha = 1.f, rsum = 0.f;
-        uint32_t pk[BN / 2];
+        uint32_t pk[HALF_COLS / 2];
         bool fast = j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY);
         if (fast) {
-          if (need_mask) exp_pass<T, ALIBI, 0>(xr, pk, scale2, -m_ref, rsum);
-          else exp_pass<T, ALIBI, kPolyPerEight>(xr, pk, scale2, -m_ref, rsum);
-          fast = !__any_sync(0xffffffffu, !(rsum <= kRowSumBound));
+          exp_pass<T, ALIBI>(xr, pk, scale2, -m_ref, rsum);
+          fast = __all_sync(0xffffffffu, rsum <= kRowSumBound);
         }
         if (!fast) {
           float mx = row_max(xr);
-          if (!ALIBI) mx *= scale2;
+          if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
           const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
           const float m_next = bump ? mx : m_ref;
           alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
@@ -535,59 +578,81 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t o[32];
-              tmem_ld32(tmem + lane_base + C::COL_O + c * 32, o);
+              tmem_ld32(o_tmem + c * 32, o);
               tmem_wait_ld();
 #pragma unroll
               for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(tmem + lane_base + C::COL_O + c * 32, o);
+              tmem_st32(o_tmem + c * 32, o);
             }
             tmem_wait_st();
           }
-          exp_pass<T, ALIBI, 0>(xr, pk, scale2, neg_m, rsum);
+          exp_pass<T, ALIBI>(xr, pk, scale2, neg_m, rsum);
         }
-        l_sum = l_sum * alpha + rsum;
-        tmem_st32(s_tmem, &pk[0]);
-        tmem_st32(s_tmem + 32, &pk[32]);
+        l_part = l_part * alpha + rsum;
+        tmem_st32(s_tmem + half * HALF_COLS, pk);   // P_h over the first half of the thread's own S columns
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&bars->p_full[t]);
+        mbar_arrive(&bars->p_full[t][half]);
       }
 
-      // Epilogue: read the row of O out of TMEM, hand the accumulator back to the MMA warp, then
-      // O / l -> global; L = m + log(l).
+      // Epilogue.  The two halves of a row meet: they exchange (reference maximum, row sum), each
+      // merges its half of the output columns from both accumulators,
+      //   O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)),  m = max(m_0, m_1),
+      // hands the accumulators back to the MMA warp and stores; L = m + log(l).
       if (!alive) break;
-      uint32_t o[D];
       if (n_tiles > 0) {
         const int gl = g + n_tiles - 1;
         if (!mbar_wait(&bars->pv_done[gl & 1], (gl >> 1) & 1, abort_flag)) { alive = false; break; }
         tc_fence_after_sync();
+      }
+      bars->xchg[tid] = m_ref;
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      const float m_other = bars->xchg[tid ^ BM];
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      bars->xchg[tid] = l_part;
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      const float l_other = bars->xchg[tid ^ BM];
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      const float m_all = fmaxf(m_ref, m_other);
+      const float w_mine = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_all);
+      const float w_other = (m_other == -INFINITY) ? 0.f : ex2_approx(m_other - m_all);
+      const float l_sum = l_part * w_mine + l_other * w_other;
+      const float w0 = half == 0 ? w_mine : w_other, w1 = half == 0 ? w_other : w_mine;
+      float o[D / 2];
+      if (n_tiles > 0) {
+        uint32_t o0[D / 2], o1[D / 2];
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_ld32(tmem + lane_base + C::COL_O + c * 32, &o[c * 32]);
+        for (int c = 0; c < D / 64; ++c) {
+          tmem_ld32(tmem + lane_base + C::COL_O0 + half * (D / 2) + c * 32, &o0[c * 32]);
+          tmem_ld32(tmem + lane_base + C::COL_O1 + half * (D / 2) + c * 32, &o1[c * 32]);
+        }
         tmem_wait_ld();
         tc_fence_before_sync();
         mbar_arrive(&bars->o_free);
+#pragma unroll
+        for (int i = 0; i < D / 2; ++i) o[i] = __uint_as_float(o0[i]) * w0 + __uint_as_float(o1[i]) * w1;
       } else {
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0u;
+        for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
       }
       {
         const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
         const float inv = 1.f / safe_l;
         T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +
-                  (int64_t)row * a.o_stride[2];
+                  (int64_t)row * a.o_stride[2] + half * (D / 2);
         if (row < p.N_q) {
 #pragma unroll
-          for (int q8 = 0; q8 < D / 8; ++q8) {
+          for (int q8 = 0; q8 < D / 16; ++q8) {
             uint4 v;
-            v.x = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 0]) * inv, __uint_as_float(o[q8 * 8 + 1]) * inv);
-            v.y = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 2]) * inv, __uint_as_float(o[q8 * 8 + 3]) * inv);
-            v.z = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 4]) * inv, __uint_as_float(o[q8 * 8 + 5]) * inv);
-            v.w = Pack2<T>::run(__uint_as_float(o[q8 * 8 + 6]) * inv, __uint_as_float(o[q8 * 8 + 7]) * inv);
+            v.x = Pack2<T>::run(o[q8 * 8 + 0] * inv, o[q8 * 8 + 1] * inv);
+            v.y = Pack2<T>::run(o[q8 * 8 + 2] * inv, o[q8 * 8 + 3] * inv);
+            v.z = Pack2<T>::run(o[q8 * 8 + 4] * inv, o[q8 * 8 + 5] * inv);
+            v.w = Pack2<T>::run(o[q8 * 8 + 6] * inv, o[q8 * 8 + 7] * inv);
             *reinterpret_cast<uint4*>(orow + q8 * 8) = v;
           }
-          if (a.lse != nullptr)
+          if (a.lse != nullptr && half == 0)
             a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
-                m_ref * kLn2 + logf(safe_l);
+                m_all * kLn2 + logf(safe_l);
         }
       }
       if (n_tiles > 0) {
@@ -595,11 +660,10 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         ++qi;
       }
     }
-  } else if (ROT_K && warp == 7) {
+  } else if (ROT_K && warp == WARP_ROTATE) {
     // ============================== K rotation warp ==============================
-    // One warp (eight warps per CTA keep 255 registers per thread available to the softmax
-    // group); each thread rotates four key rows of the tile.
-    const int r0 = tid - 224;
+    // One warp; each thread rotates four key rows of the tile.
+    const int r0 = lane;
     Item it;
     int g = 0;
     bool ok = true;
@@ -628,7 +692,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, AF_STATUS_WAIT_TIMEOUT);
-  if (warp == 4) {
+  if (warp == WARP_PRODUCER) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem, C::TMEM_COLS);
@@ -648,7 +712,7 @@ int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 256 : 224, smem, st>>>(args, mq, mk, mv);
+  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 384 : 352, smem, st>>>(args, mq, mk, mv);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
 }
