@@ -56,60 +56,94 @@ bool tma_ok(const void* ptr, int B, int H, int N, const int64_t* st) {
 
 // RoPE pre-pass: dst[b, h, n, :] = rope(src[b, h, n, :]) as contiguous (B, H, N, D) for Q and K
 // in one launch; fp32 math, one rounding to T -- the same arithmetic as the in-kernel rotation.
-// One thread per pair of 16-byte chunks (d, d + D/2).
+// A thread owns one pair of 16-byte chunks (d, d + D/2) of one position n of one batch entry,
+// loads that position's cos / sin once and walks all heads of Q, then of K, four heads per
+// step so that eight 16-byte loads are in flight per thread: the traffic is the tensors
+// themselves plus one read of the tables per batch entry.
 struct RotateJob {
-  const void* src; void* dst;
+  const void* src; void* dst;   // dst == nullptr: nothing to do
   int64_t s0, s1, s2;
   int H, N;
-  int64_t chunks;   // B * H * N * (D / 16)
 };
 
-template <typename T, int D>
-__global__ void rope_prepass_kernel(const RotateJob jq, const RotateJob jk, const T* __restrict__ cos_,
-                                    const T* __restrict__ sin_, int64_t sr) {
-  constexpr int HC = D / 16;
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool is_q = idx < jq.chunks;
-  const RotateJob& job = is_q ? jq : jk;
-  if (!is_q) idx -= jq.chunks;
-  if (idx >= job.chunks) return;
-  const int c = (int)(idx % HC);
-  const int64_t row = idx / HC;
-  const int n = (int)(row % job.N);
-  const int h = (int)((row / job.N) % job.H);
-  const int64_t b = row / ((int64_t)job.N * job.H);
-  const T* src = reinterpret_cast<const T*>(job.src) + b * job.s0 + (int64_t)h * job.s1 + (int64_t)n * job.s2;
-  T* dst = reinterpret_cast<T*>(job.dst) + row * D;
-  const uint4 xl = *reinterpret_cast<const uint4*>(src + c * 8), xh = *reinterpret_cast<const uint4*>(src + D / 2 + c * 8);
-  const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + c * 8));
-  const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + D / 2 + c * 8));
-  const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + c * 8));
-  const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + D / 2 + c * 8));
+template <typename T>
+__device__ __forceinline__ void rotate_pair(const uint4& xl, const uint4& xh, const uint4& cl, const uint4& ch,
+                                            const uint4& sl, const uint4& sh, uint4& ol, uint4& oh) {
   const uint32_t xlw[4] = {xl.x, xl.y, xl.z, xl.w}, xhw[4] = {xh.x, xh.y, xh.z, xh.w};
   const uint32_t clw[4] = {cl.x, cl.y, cl.z, cl.w}, chw[4] = {ch.x, ch.y, ch.z, ch.w};
   const uint32_t slw[4] = {sl.x, sl.y, sl.z, sl.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
-  uint32_t ol[4], oh[4];
+  uint32_t lo[4], hi[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float2 x1 = Pack2<T>::unpack(xlw[i]), x2 = Pack2<T>::unpack(xhw[i]);
     const float2 c1 = Pack2<T>::unpack(clw[i]), c2 = Pack2<T>::unpack(chw[i]);
     const float2 s1v = Pack2<T>::unpack(slw[i]), s2v = Pack2<T>::unpack(shw[i]);
-    ol[i] = Pack2<T>::run(x1.x * c1.x - x2.x * s1v.x, x1.y * c1.y - x2.y * s1v.y);
-    oh[i] = Pack2<T>::run(x2.x * c2.x + x1.x * s2v.x, x2.y * c2.y + x1.y * s2v.y);
+    lo[i] = Pack2<T>::run(x1.x * c1.x - x2.x * s1v.x, x1.y * c1.y - x2.y * s1v.y);
+    hi[i] = Pack2<T>::run(x2.x * c2.x + x1.x * s2v.x, x2.y * c2.y + x1.y * s2v.y);
   }
-  *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
-  *reinterpret_cast<uint4*>(dst + D / 2 + c * 8) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+  ol = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+  oh = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+}
+
+template <typename T, int D>
+__device__ __forceinline__ void rotate_heads(const RotateJob& job, int64_t b, int n, int c, const uint4& cl,
+                                             const uint4& ch, const uint4& sl, const uint4& sh) {
+  if (job.dst == nullptr || n >= job.N) return;
+  const T* src = reinterpret_cast<const T*>(job.src) + b * job.s0 + (int64_t)n * job.s2 + c * 8;
+  T* dst = reinterpret_cast<T*>(job.dst) + ((b * job.H) * (int64_t)job.N + n) * D + c * 8;
+  const int64_t dst_h = (int64_t)job.N * D;
+  int h = 0;
+  for (; h + 4 <= job.H; h += 4) {
+    uint4 xl[4], xh[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xl[u] = *reinterpret_cast<const uint4*>(src + (h + u) * job.s1);
+      xh[u] = *reinterpret_cast<const uint4*>(src + (h + u) * job.s1 + D / 2);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint4 ol, oh;
+      rotate_pair<T>(xl[u], xh[u], cl, ch, sl, sh, ol, oh);
+      *reinterpret_cast<uint4*>(dst + (h + u) * dst_h) = ol;
+      *reinterpret_cast<uint4*>(dst + (h + u) * dst_h + D / 2) = oh;
+    }
+  }
+  for (; h < job.H; ++h) {
+    const uint4 xl = *reinterpret_cast<const uint4*>(src + h * job.s1);
+    const uint4 xh = *reinterpret_cast<const uint4*>(src + h * job.s1 + D / 2);
+    uint4 ol, oh;
+    rotate_pair<T>(xl, xh, cl, ch, sl, sh, ol, oh);
+    *reinterpret_cast<uint4*>(dst + h * dst_h) = ol;
+    *reinterpret_cast<uint4*>(dst + h * dst_h + D / 2) = oh;
+  }
+}
+
+template <typename T, int D>
+__global__ void rope_prepass_kernel(const RotateJob jq, const RotateJob jk, const T* __restrict__ cos_,
+                                    const T* __restrict__ sin_, int64_t sr, int n_max) {
+  constexpr int HC = D / 16;                       // chunk pairs per row
+  const int c = threadIdx.x % HC;
+  const int n = blockIdx.x * (blockDim.x / HC) + threadIdx.x / HC;
+  const int64_t b = blockIdx.y;
+  if (n >= n_max) return;
+  const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + c * 8));
+  const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + D / 2 + c * 8));
+  const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + c * 8));
+  const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + D / 2 + c * 8));
+  rotate_heads<T, D>(jq, b, n, c, cl, ch, sl, sh);
+  rotate_heads<T, D>(jk, b, n, c, cl, ch, sl, sh);
 }
 
 template <typename T, int D>
 int launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st) {
-  RotateJob jq{p.q, q_out, p.q_stride[0], p.q_stride[1], p.q_stride[2], p.H_q, p.N_q,
-               (int64_t)p.B * p.H_q * p.N_q * (D / 16)};
-  RotateJob jk{p.k, k_out, p.k_stride[0], p.k_stride[1], p.k_stride[2], p.H_kv, p.N_kv,
-               (int64_t)p.B * p.H_kv * p.N_kv * (D / 16)};
-  const int64_t total = jq.chunks + jk.chunks;
-  rope_prepass_kernel<T, D><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
-      jq, jk, reinterpret_cast<const T*>(p.cos), reinterpret_cast<const T*>(p.sin), p.rope_stride_n);
+  RotateJob jq{p.q, q_out, p.q_stride[0], p.q_stride[1], p.q_stride[2], p.H_q, p.N_q};
+  RotateJob jk{p.k, k_out, p.k_stride[0], p.k_stride[1], p.k_stride[2], p.H_kv, p.N_kv};
+  const int n_max = p.N_q > p.N_kv ? p.N_q : p.N_kv;
+  constexpr int THREADS = 128, ROWS = THREADS / (D / 16);
+  AF_REQUIRE(p.B <= 65535, "batch exceeds the launch grid limit");
+  const dim3 grid((unsigned)((n_max + ROWS - 1) / ROWS), (unsigned)p.B);
+  rope_prepass_kernel<T, D><<<grid, THREADS, 0, st>>>(jq, jk, reinterpret_cast<const T*>(p.cos),
+                                                      reinterpret_cast<const T*>(p.sin), p.rope_stride_n, n_max);
   count_launch();
   return check_cuda(cudaGetLastError(), "rope_prepass launch");
 }
