@@ -84,6 +84,33 @@ __global__ void bwd_delta_kernel(const AfBwdParams a) {
   if (lane == 0) a.delta[warp] = s;
 }
 
+// Vector form for 2-byte element types with unit inner strides and 16-byte-aligned rows: LPR
+// lanes per row, each with one 16-byte load of O and of dO (8 elements), so that the launch is
+// bound by HBM bandwidth rather than by load instructions.
+template <typename T, int LPR>
+__global__ void bwd_delta_vec_kernel(const AfBwdParams a) {
+  const AfProblem& p = a.p;
+  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = gthread / LPR;
+  const int sub = (int)(gthread % LPR);
+  const int64_t total = (int64_t)p.B * p.H_q * p.N_q;
+  float s = 0.f;
+  if (r < total) {
+    const int row = (int)(r % p.N_q), h = (int)((r / p.N_q) % p.H_q);
+    const int64_t b = r / ((int64_t)p.N_q * p.H_q);
+    const T* o = reinterpret_cast<const T*>(a.o) + b * a.o_stride[0] + (int64_t)h * a.o_stride[1] + (int64_t)row * a.o_stride[2] + sub * 8;
+    const T* g = reinterpret_cast<const T*>(a.d_o) + b * a.do_stride[0] + (int64_t)h * a.do_stride[1] + (int64_t)row * a.do_stride[2] + sub * 8;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o), gv = *reinterpret_cast<const uint4*>(g);
+    const T* oe = reinterpret_cast<const T*>(&ov);
+    const T* ge = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += Elem<T>::to_f32(oe[i]) * Elem<T>::to_f32(ge[i]);
+  }
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (sub == 0 && r < total) a.delta[r] = s;
+}
+
 // Recompute one 32x32 tile of P and dS into shared memory.  Thread (ty, tx) owns query rows
 // 4*ty..4*ty+3 and keys tx, tx+16.
 template <typename T, int LD>
@@ -442,6 +469,22 @@ int launch_dtype(const AfBwdParams& a, cudaStream_t st) {
 int launch_bwd_delta(const AfBwdParams& a, cudaStream_t st) {
   const int64_t rows = (int64_t)a.p.B * a.p.H_q * a.p.N_q;
   if (rows <= 0) return AF_OK;
+  const AfProblem& p = a.p;
+  const bool aligned = a.o_stride[3] == 1 && a.do_stride[3] == 1 && ((uintptr_t)a.o & 15) == 0 && ((uintptr_t)a.d_o & 15) == 0 &&
+                       a.o_stride[0] % 8 == 0 && a.o_stride[1] % 8 == 0 && a.o_stride[2] % 8 == 0 &&
+                       a.do_stride[0] % 8 == 0 && a.do_stride[1] % 8 == 0 && a.do_stride[2] % 8 == 0;
+  if (aligned && p.dtype != AF_F32 && (p.D == 64 || p.D == 128 || p.D == 256)) {
+    const int lpr = p.D / 8;
+    const unsigned vblocks = (unsigned)((rows * lpr + 255) / 256);
+#define AF_DELTA_VEC(TYPE)                                                                  \
+    if (lpr == 8) bwd_delta_vec_kernel<TYPE, 8><<<vblocks, 256, 0, st>>>(a);                \
+    else if (lpr == 16) bwd_delta_vec_kernel<TYPE, 16><<<vblocks, 256, 0, st>>>(a);         \
+    else bwd_delta_vec_kernel<TYPE, 32><<<vblocks, 256, 0, st>>>(a);
+    if (p.dtype == AF_F16) { AF_DELTA_VEC(__half) } else { AF_DELTA_VEC(__nv_bfloat16) }
+#undef AF_DELTA_VEC
+    count_launch();
+    return check_cuda(cudaGetLastError(), "bwd_delta launch");
+  }
   const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
   switch (a.p.dtype) {
     case AF_F16: bwd_delta_kernel<__half><<<blocks, 256, 0, st>>>(a); break;
