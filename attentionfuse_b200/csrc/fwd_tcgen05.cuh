@@ -97,12 +97,13 @@ struct TcArgs {
 // Which key tiles a query tile visits.
 struct TileWalk {
   int n_tiles;
-  int first_tile;            // dense / causal / window: tile index of step 0
+  int first_tile;            // dense / causal / window: lowest tile index
+  int step;                  // +1, or -1 when the tiles are walked from the diagonal down
   const int32_t* list;       // block lists: active key blocks of this query block
   int per_block;
   __device__ __forceinline__ int key0(int j) const {
     if (list != nullptr) return (list[j / per_block] * per_block + (j % per_block)) * BN;
-    return (first_tile + j) * BN;
+    return (first_tile + (step > 0 ? j : n_tiles - 1 - j)) * BN;
   }
 };
 
@@ -111,6 +112,10 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   w.list = nullptr;
   w.per_block = 1;
   w.first_tile = 0;
+  // Causal + ALiBi: the bias grows towards the diagonal by slope * 128 per tile, so walking up
+  // would raise the row maximum (and rescale the accumulator) at every tile; walking down from
+  // the diagonal sets the reference in the first tile and every later tile stays below it.
+  w.step = (p.mask_kind == AF_MASK_CAUSAL && p.bias_kind == AF_BIAS_ALIBI) ? -1 : 1;
   const int m0 = m_blk * BM;
   const int m_end = min(m0 + BM, p.N_q);
   if (p.mask_kind == AF_MASK_BLOCKS) {
@@ -275,11 +280,14 @@ __device__ __forceinline__ float row_max(const uint32_t (&xr)[NC]) {
   return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 }
 
-// P = 2^(x * scale2 + neg_m) (ALiBi rows are already scaled: 2^(x + neg_m)) packed to T, and the
-// row sum of the unrounded values.
-template <typename T, bool PRESCALED, int NC>
-__device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk)[NC / 2], float scale2, float neg_m,
-                                         float& rsum) {
+// P = 2^y packed to T and the row sum of the unrounded values, with
+//   EXP_SCALE      y = x * scale2 + shift
+//   EXP_AFFINE     y = x * scale2 + slope_c * c + shift     (ALiBi folded in, c = column index)
+//   EXP_PRESCALED  y = x + shift                            (scores already scaled and biased)
+enum { EXP_SCALE = 0, EXP_AFFINE = 1, EXP_PRESCALED = 2 };
+template <typename T, int KIND, int NC>
+__device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk)[NC / 2], float scale2, float shift,
+                                         float slope_c, float& rsum) {
   float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int c = 0; c < NC; c += 4) {
@@ -287,7 +295,11 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const float x = __uint_as_float(xr[c + u]);
-      e[u] = ex2_approx(PRESCALED ? x + neg_m : fmaf(x, scale2, neg_m));
+      float y;
+      if (KIND == EXP_PRESCALED) y = x + shift;
+      else if (KIND == EXP_AFFINE) y = fmaf(x, scale2, fmaf(slope_c, (float)(c + u), shift));
+      else y = fmaf(x, scale2, shift);
+      e[u] = ex2_approx(y);
       rs4[u] += e[u];
     }
     pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
@@ -543,11 +555,18 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
             xr[c] = keep ? xr[c] : 0xff800000u;     // -inf
           }
         }
+        // ALiBi: the bias -slope |rel - c| is affine in the column, slope_c * c + bias0, wherever the
+        // sign of rel - c is the same for all of the thread's visible columns: always under a
+        // causal mask (visible columns have c <= rel), otherwise for threads whose row lies on
+        // one side of their 64 columns.  Then the bias rides along in the exponent pass as one
+        // more FMA; a warp with a row inside its columns takes the classic order below.
+        float slope_c = 0.f, bias0 = 0.f;
+        bool affine = true;
         if (ALIBI) {
-          const float relf = (float)rel;
-#pragma unroll
-          for (int c = 0; c < HALF_COLS; ++c)
-            xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
+          const bool below = (EMASK == EMASK_CAUSAL) || rel >= HALF_COLS - 1;
+          affine = (EMASK == EMASK_CAUSAL) || __all_sync(0xffffffffu, below || rel <= 0);
+          slope_c = below ? slope2 : -slope2;
+          bias0 = -slope_c * (float)rel;
         }
         // Usual case: this half of the row already has a reference maximum and the tile does not
         // exceed it by much.  Then P is formed against the standing reference right away, without
@@ -557,12 +576,18 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         // first, reference update, accumulator rescale, then P.
         float alpha = 1.f, rsum = 0.f;
         uint32_t pk[HALF_COLS / 2];
-        bool fast = j > 0 && __all_sync(0xffffffffu, m_ref != -INFINITY);
+        bool fast = j > 0 && affine && __all_sync(0xffffffffu, m_ref != -INFINITY);
         if (fast) {
-          exp_pass<T, ALIBI>(xr, pk, scale2, -m_ref, rsum);
+          exp_pass<T, ALIBI ? EXP_AFFINE : EXP_SCALE>(xr, pk, scale2, bias0 - m_ref, slope_c, rsum);
           fast = __all_sync(0xffffffffu, rsum <= kRowSumBound);
         }
         if (!fast) {
+          if (ALIBI) {
+            const float relf = (float)rel;
+#pragma unroll
+            for (int c = 0; c < HALF_COLS; ++c)
+              xr[c] = __float_as_uint(fmaf(__uint_as_float(xr[c]), scale2, -slope2 * fabsf(relf - (float)c)));
+          }
           float mx = row_max(xr);
           if (!ALIBI) mx *= scale2;                   // the maximum commutes with the positive scale
           const bool bump = mx > m_ref + kRescaleThreshold;   // also true for the first finite max
@@ -586,7 +611,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
             }
             tmem_wait_st();
           }
-          exp_pass<T, ALIBI>(xr, pk, scale2, neg_m, rsum);
+          exp_pass<T, ALIBI ? EXP_PRESCALED : EXP_SCALE>(xr, pk, scale2, neg_m, 0.f, rsum);
         }
         l_part = l_part * alpha + rsum;
         tmem_st32(s_tmem + half * HALF_COLS, pk);   // P_h over the first half of the thread's own S columns

@@ -246,11 +246,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip fwd+bwd / decode side measurements")
+    ap.add_argument("--sweep", choices=["cfg2", "cfg3", "cfg5"],
+                    help="time the other configurations of the baseline (one JSON line per case) instead of the bench line")
     ap.add_argument("--profile-case", choices=["fwd", "bwd", "decode"],
                     help="run three iterations of a small case of one kernel family and exit (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
         return profile_case(args.profile_case)
+    if args.sweep:
+        return sweep(args.sweep)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
@@ -389,6 +393,114 @@ def main():
     if dist_on:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _median_ms(fn, warmup=5, iters=20):
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); fn(); e.record(); torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def sweep(which: str):
+    """The baseline's other configurations on one GPU, median of per-call CUDA-event times, one JSON
+    line per case.  cfg2: forward sweep [4,12,N,64], six compositions, bf16 and f16.  cfg3: decode,
+    three head geometries x four cache lengths, lengths U[L/2, L].  cfg5: BigBird-style per-head
+    block masks [2,16,8192,64] f16, forward and forward+backward, with the all-active control."""
+    import numpy as np
+    import attentionfuse_b200 as af
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode, decode_workspace, _pick_num_splits
+    from oracle import attention_oracle as orc
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(2000)
+    pk, _ = peaks()
+
+    def rnd(*shape, dt):
+        return torch.randn(*shape, generator=gen, device=dev, dtype=dt)
+
+    if which == "cfg2":
+        B, H, D, W = 4, 12, 64, 256
+        sdp = af.scaled_dot_product
+        fns = {
+            "dense": (af.attention(lambda Q, K, V: af.softmax(sdp(Q, K)) @ V), "dense", False),
+            "causal": (af.attention(lambda Q, K, V: af.softmax(af.causal(sdp(Q, K))) @ V), "causal", False),
+            "window256": (af.attention(lambda Q, K, V: af.softmax(af.sliding_window(sdp(Q, K), W)) @ V), "window", False),
+            "causal+alibi": (af.attention(lambda Q, K, V: af.softmax(af.causal(af.alibi(sdp(Q, K), H))) @ V), "causal", False),
+            "causal+rope": (af.attention(lambda Q, K, V: af.softmax(af.causal(af.rope(Q, K))) @ V), "causal", True),
+            "causal+rope+alibi": (af.attention(lambda Q, K, V: af.softmax(af.causal(af.alibi(af.rope(Q, K), H))) @ V), "causal", True),
+        }
+        for dt in (torch.bfloat16, torch.float16):
+            for N in (512, 1024, 2048, 4096):
+                Q, K, V = rnd(B, H, N, D, dt=dt), rnd(B, H, N, D, dt=dt), rnd(B, H, N, D, dt=dt)
+                cos, sin = (t.to(dev) for t in orc.build_rope_cache(N, D, 10000.0, dt))
+                for name, (fn, kind, rope) in fns.items():
+                    kw = dict(cos=cos, sin=sin) if rope else {}
+                    ms = _median_ms(lambda: fn(Q, K, V, **kw))
+                    pairs = {"dense": N * N, "causal": causal_pairs(N), "window": N * (2 * W - 1) - W * (W - 1)}[kind]
+                    tf = 4.0 * B * H * D * pairs / (ms * 1e-3) / 1e12
+                    print(json.dumps({"sweep": "cfg2", "dtype": str(dt).split(".")[-1], "N": N, "variant": name,
+                                      "ms": round(ms, 4), "tflops": round(tf, 1),
+                                      "frac_of_measured_peak": round(tf / pk["bf16_tflops"], 3)}), flush=True)
+    elif which == "cfg3":
+        B, D, dt = 16, 128, torch.bfloat16
+        for Hq, Hkv in ((32, 8), (64, 8), (64, 1)):
+            for L in (1024, 4096, 16384, 32768):
+                lens = torch.randint(L // 2, L + 1, (B,), generator=gen, device=dev, dtype=torch.int32)
+                n_buf = 4 if L < 32768 else 3     # rotate caches: no byte of a step is still in L2
+                caches = [(rnd(B, Hkv, L, D, dt=dt), rnd(B, Hkv, L, D, dt=dt)) for _ in range(n_buf)]
+                Q = rnd(B, Hq, 1, D, dt=dt)
+                out = torch.empty_like(Q)
+                it = [0]
+
+                S = _pick_num_splits(B, Hq, Hkv, L, 0)
+                ws = decode_workspace(S, B, Hq, D, dev)   # allocated once, as a serving loop would
+
+                def step():
+                    Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
+                    run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens, num_splits=S, workspace=ws)
+                ms = _median_ms(step)
+                nbytes = 2.0 * Hkv * D * 2 * float(lens.sum().item()) + 2.0 * B * Hq * D * 2
+                gbs = nbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({"sweep": "cfg3", "H_q": Hq, "H_kv": Hkv, "L": L, "ms": round(ms, 4),
+                                  "num_splits": S, "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}), flush=True)
+                del caches
+    else:
+        B, H, N, D, blk, dt = 2, 16, 8192, 64, 128, torch.float16
+        nb = N // blk
+        grids = np.zeros((H, nb, nb), dtype=bool)
+        for h in range(H):
+            rng = np.random.default_rng(5000 + h)
+            g = grids[h]
+            g[:, :2] = True
+            g[:2, :] = True
+            for i in range(nb):
+                g[i, max(0, i - 1):min(nb, i + 2)] = True
+                free = np.flatnonzero(~g[i])
+                if len(free):
+                    g[i, rng.choice(free, size=min(3, len(free)), replace=False)] = True
+        masks = {"bigbird per head": af.create_block_mask_per_head(torch.from_numpy(grids), blk, blk, device=dev),
+                 "all active (control)": af.create_block_mask_per_head(torch.ones(H, nb, nb, dtype=torch.bool), blk, blk, device=dev)}
+        fn = af.attention(lambda Q, K, V: af.softmax(af.block_sparse(af.scaled_dot_product(Q, K))) @ V)
+        Q, K, V, dO = (rnd(B, H, N, D, dt=dt) for _ in range(4))
+        Qg, Kg, Vg = (t.clone().requires_grad_(True) for t in (Q, K, V))
+        for name, bm in masks.items():
+            active = float(bm.dense_grid().float().mean().item())
+            pairs = active * N * N
+            ms_f = _median_ms(lambda: fn(Q, K, V, block_mask=bm))
+
+            def fb():
+                o = fn(Qg, Kg, Vg, block_mask=bm)
+                o.backward(dO)
+                Qg.grad = Kg.grad = Vg.grad = None
+            ms_fb = _median_ms(fb, warmup=3, iters=10)
+            print(json.dumps({"sweep": "cfg5", "mask": name, "active_fraction": round(active, 4),
+                              "fwd_ms": round(ms_f, 4), "fwd_tflops": round(4.0 * B * H * D * pairs / (ms_f * 1e-3) / 1e12, 1),
+                              "fwd_bwd_ms": round(ms_fb, 4),
+                              "fwd_bwd_tflops": round(14.0 * B * H * D * pairs / (ms_fb * 1e-3) / 1e12, 1)}), flush=True)
 
 
 def profile_case(which: str):
