@@ -152,7 +152,9 @@ int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv,
   const int group = H_q > H_kv ? H_q / H_kv : 1;
   const int64_t units = (int64_t)B * H_kv * ((group + 63) / 64);
   const int64_t slots = 2LL * sm_count * (group > 16 ? 1 : 5);
-  int64_t want = (slots + units - 1) / units;
+  // one wave must fit the resident slots (round down: one CTA too many doubles the time);
+  // several waves round up
+  int64_t want = group > 16 ? slots / units : (slots + units - 1) / units;
   const int64_t cap = N_kv / 512 > 1 ? N_kv / 512 : 1;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
