@@ -84,6 +84,10 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st);
 bool bwd_mma_supports(const AfBwdParams& a, const char** why);
 
 int launch_decode_split(const AfDecodeParams& a, cudaStream_t st);
+// Split-K decode of large head groups (MQA) on the tcgen05 forward kernel: the query heads of a KV
+// group are the rows of one query tile.  Same partials as launch_decode_split.
+bool decode_tc_supports(const AfDecodeParams& a);
+int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st);
 int launch_decode_combine(const AfDecodeParams& a, cudaStream_t st);
 int launch_decode_static(const AfDecodeParams& a, cudaStream_t st);
 int64_t decode_exchange_bytes(int world, int B, int H_q, int D);

@@ -506,6 +506,8 @@ int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
              "decode needs 16-byte aligned K/V base pointers");
   AF_REQUIRE(a.q_stride[1] % 2 == 0 && a.q_stride[0] % 2 == 0, "decode needs 4-byte aligned Q rows");
   AF_REQUIRE(a.bias_kind == AF_BIAS_NONE || (a.bias_kind == AF_BIAS_ALIBI && a.slopes), "bad bias_kind for decode");
+  // more than 16 query heads per KV head: tensor-bound on mma.sync, so the tcgen05 kernel takes it
+  if (decode_tc_supports(a)) return launch_decode_split_tc(a, st);
   if (a.dtype == AF_F16) return a.D == 64 ? launch_split_impl<__half, 64>(a, st) : launch_split_impl<__half, 128>(a, st);
   return a.D == 64 ? launch_split_impl<__nv_bfloat16, 64>(a, st) : launch_split_impl<__nv_bfloat16, 128>(a, st);
 }

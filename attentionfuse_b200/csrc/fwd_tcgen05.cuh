@@ -90,13 +90,23 @@ struct TcArgs {
   int num_m_blocks;
   int kv_tiles_per_block;   // block_n / 128 for block lists
   int q_tiles_per_block;    // block_m / 128
-  int total_items;          // num_m_blocks * B * H_q query tiles
+  int total_items;          // num_m_blocks * B * H_q query tiles (split mode: num_splits * B * H)
   int grid_ctas;            // CTAs to launch: one per SM (persistent) or one per item
+  // Split-K decode mode (num_splits > 0): the "query rows" of an item are the query heads of one
+  // KV group (N_q = group size, one pseudo-head per KV head), the keys of a sequence are dealt out
+  // to num_splits items, and the epilogue writes un-normalised partials (m, l, acc) for the
+  // combine kernel instead of O.  Row index of the partials: (split * B + b) * H_total + head.
+  int num_splits;
+  const int32_t* kv_lens;   // optional per-batch valid key count
+  float* ws_m;
+  float* ws_l;
+  float* ws_acc;
 };
 
 // Which key tiles a query tile visits.
 struct TileWalk {
   int n_tiles;
+  int n_kv;                  // keys of this item's sequence (split mode: the batch entry's valid length)
   int first_tile;            // dense / causal / window: lowest tile index
   int step;                  // +1, or -1 when the tiles are walked from the diagonal down
   const int32_t* list;       // block lists: active key blocks of this query block
@@ -116,6 +126,7 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   // would raise the row maximum (and rescale the accumulator) at every tile; walking down from
   // the diagonal sets the reference in the first tile and every later tile stays below it.
   w.step = (p.mask_kind == AF_MASK_CAUSAL && p.bias_kind == AF_BIAS_ALIBI) ? -1 : 1;
+  w.n_kv = p.N_kv;
   const int m0 = m_blk * BM;
   const int m_end = min(m0 + BM, p.N_q);
   if (p.mask_kind == AF_MASK_BLOCKS) {
@@ -140,6 +151,7 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
 // One work item = one 128-row query tile of one (batch, query head).
 struct Item {
   int m0, b, h, h_kv;
+  int split;                 // split mode: which share of the keys
   TileWalk walk;
 };
 
@@ -155,11 +167,25 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
   const int w = (int)w64;
   const AfProblem& p = args.a.p;
   const int bh_count = p.B * p.H_q;
-  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - w / bh_count) : (w / bh_count);
   const int bh = w % bh_count;
   it.b = bh / p.H_q;
   it.h = bh % p.H_q;
   it.h_kv = it.h / (p.H_q / p.H_kv);
+  it.split = 0;
+  if (args.num_splits > 0) {
+    // split-K decode: one query tile per (batch, pseudo-head); the 128-key tiles of the valid
+    // length are dealt out evenly to the splits
+    it.split = w / bh_count;
+    it.m0 = 0;
+    TileWalk& wk = it.walk;
+    wk.list = nullptr; wk.per_block = 1; wk.step = 1;
+    wk.n_kv = args.kv_lens ? min(max(args.kv_lens[it.b], 0), p.N_kv) : p.N_kv;
+    const int tiles = (wk.n_kv + BN - 1) / BN;
+    wk.first_tile = (int)((int64_t)it.split * tiles / args.num_splits);
+    wk.n_tiles = (int)((int64_t)(it.split + 1) * tiles / args.num_splits) - wk.first_tile;
+    return true;
+  }
+  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - w / bh_count) : (w / bh_count);
   it.m0 = m_blk * BM;
   it.walk = make_walk(p, args, m_blk, it.h);
   return true;
@@ -539,14 +565,14 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         tmem_wait_ld();
 
         // Tile-level decision: only edge / diagonal tiles pay for element masking.
-        bool need_mask = key0 + BN > p.N_kv;
+        bool need_mask = key0 + BN > walk.n_kv;
         if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
         if (EMASK == EMASK_WINDOW)
           need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
         const int col0 = key0 + half * HALF_COLS;   // key index of this thread's column 0
         const int rel = row - col0;                 // column c is kept iff ...
         if (need_mask) {
-          const int kmax = p.N_kv - col0;           // ... c < kmax
+          const int kmax = walk.n_kv - col0;        // ... c < kmax
 #pragma unroll
           for (int c = 0; c < HALF_COLS; ++c) {
             bool keep = c < kmax;
@@ -614,6 +640,21 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           exp_pass<T, ALIBI ? EXP_PRESCALED : EXP_SCALE>(xr, pk, scale2, neg_m, 0.f, rsum);
         }
         l_part = l_part * alpha + rsum;
+        if (args.num_splits > 0 && key0 + BN > walk.n_kv) {
+          // Split-K decode: cache rows past the valid length hold whatever the allocation held
+          // (TMA zero-fills only past the tensor's extent) and 0 * NaN would poison O, so the
+          // softmax threads clear those V rows of the stage before they release P.
+          const int s = gg % STAGES;
+          if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { alive = false; break; }
+          // each half clears the rows its own P.V product reads (keys [64 half, 64 half + 64))
+          const int first = max(walk.n_kv - key0, half * HALF_COLS), last = (half + 1) * HALF_COLS;
+          const uint32_t v_tile = sV0 + s * C::TILE_BYTES;
+          for (int idx = rtid; idx < (last - first) * C::PANELS * 8; idx += BM) {
+            const int r = first + idx / (C::PANELS * 8), rem = idx % (C::PANELS * 8);
+            sts128(v_tile + (rem >> 3) * PANEL_BYTES + r * 128 + ((rem & 7) << 4), make_uint4(0u, 0u, 0u, 0u));
+          }
+          fence_proxy_async_smem();
+        }
         tmem_st32(s_tmem + half * HALF_COLS, pk);   // P_h over the first half of the thread's own S columns
         tmem_wait_st();
         tc_fence_before_sync();
@@ -660,7 +701,19 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
       }
-      {
+      if (args.num_splits > 0) {
+        // split-K decode: un-normalised partial of this (split, batch, head) for the combine kernel
+        if (row < p.N_q) {
+          const int64_t wr = ((int64_t)it.split * p.B + b) * ((int64_t)p.H_q * p.N_q) + (int64_t)h * p.N_q + row;
+          float4* dst = reinterpret_cast<float4*>(args.ws_acc + wr * D + half * (D / 2));
+#pragma unroll
+          for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_float4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
+          if (half == 0) {
+            args.ws_m[wr] = m_all * kLn2;      // -inf when the split saw no key
+            args.ws_l[wr] = l_sum;
+          }
+        }
+      } else {
         const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
         const float inv = 1.f / safe_l;
         T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +

@@ -200,7 +200,7 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   if (!fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why))
     return fail(AF_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
   const AfProblem& p = a.p;
-  tc::TcArgs args;
+  tc::TcArgs args{};
   args.a = a;
   args.num_m_blocks = (p.N_q + tc::BM - 1) / tc::BM;
   args.kv_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_n / tc::BN : 1;
@@ -246,6 +246,63 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   }
   if (mode == tc::ROPE_NONE) return tc::launch_d128_norope(p.dtype, args, mq, mk, mv, st);
   return tc::launch_d128_fused(p.dtype, args, mq, mk, mv, st);
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-K decode on the forward kernel.  With more than 16 query heads per KV head (MQA) the
+// mma.sync decode kernel is bound by the legacy tensor path; here the heads of a group are the
+// rows of a 128-row query tile (Q viewed as (B, H_kv, group, D)), every (split, batch, kv head)
+// is one work item of the persistent kernel, and its epilogue writes the un-normalised partials.
+// ---------------------------------------------------------------------------------------
+static void decode_q_view(const AfDecodeParams& a, int64_t out[4]) {
+  const int group = a.H_q / a.H_kv;
+  out[0] = a.q_stride[0]; out[1] = (int64_t)group * a.q_stride[1]; out[2] = a.q_stride[1]; out[3] = a.q_stride[3];
+}
+
+bool decode_tc_supports(const AfDecodeParams& a) {
+  if (a.H_kv < 1 || a.H_q % a.H_kv != 0) return false;
+  const int group = a.H_q / a.H_kv;
+  if (group <= 16 || group > tc::BM) return false;   // small groups: the bandwidth-tuned mma.sync kernel
+  if (a.dtype != AF_F16 && a.dtype != AF_BF16) return false;
+  if (a.D != 64 && a.D != 128) return false;
+  if (a.bias_kind != AF_BIAS_NONE || !(a.sm_scale > 0.f) || a.N_kv < 1 || a.num_splits < 1) return false;
+  if (a.ws_acc == nullptr || ((uintptr_t)a.ws_acc & 15) != 0) return false;
+  int64_t qs[4];
+  decode_q_view(a, qs);
+  return tma_ok(a.q, a.B, a.H_kv, group, qs) && tma_ok(a.k, a.B, a.H_kv, a.N_kv, a.k_stride) &&
+         tma_ok(a.v, a.B, a.H_kv, a.N_kv, a.v_stride);
+}
+
+int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st) {
+  AF_REQUIRE(decode_tc_supports(a), "tcgen05 decode does not support this problem");
+  const int group = a.H_q / a.H_kv;
+  int64_t qs[4];
+  decode_q_view(a, qs);
+  tc::TcArgs args{};
+  AfProblem& p = args.a.p;
+  p.dtype = a.dtype;
+  p.B = a.B; p.H_q = a.H_kv; p.H_kv = a.H_kv; p.N_q = group; p.N_kv = a.N_kv; p.D = a.D;
+  p.sm_scale = a.sm_scale;
+  p.mask_kind = AF_MASK_FULL; p.bias_kind = AF_BIAS_NONE; p.norm_kind = AF_NORM_SOFTMAX;
+  p.status = a.status;
+  args.num_m_blocks = 1;
+  args.kv_tiles_per_block = args.q_tiles_per_block = 1;
+  args.num_splits = a.num_splits;
+  args.kv_lens = a.kv_lens;
+  args.ws_m = a.ws_m; args.ws_l = a.ws_l; args.ws_acc = a.ws_acc;
+  AF_REQUIRE((int64_t)a.num_splits * a.B * a.H_kv <= 0x7fffffff, "too many items for one launch");
+  args.total_items = a.num_splits * a.B * a.H_kv;
+  int dev = 0, sms = 0;
+  AF_CUDA_OK(cudaGetDevice(&dev));
+  AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((rc = make_map(&mq, a.dtype, a.q, a.B, a.H_kv, group, a.D, qs)) != AF_OK) return rc;
+  if ((rc = make_map(&mk, a.dtype, a.k, a.B, a.H_kv, a.N_kv, a.D, a.k_stride)) != AF_OK) return rc;
+  if ((rc = make_map(&mv, a.dtype, a.v, a.B, a.H_kv, a.N_kv, a.D, a.v_stride)) != AF_OK) return rc;
+  if (a.D == 64) return tc::launch_d64_norope(a.dtype, args, mq, mk, mv, st);
+  return tc::launch_d128_norope(a.dtype, args, mq, mk, mv, st);
 }
 
 }  // namespace af

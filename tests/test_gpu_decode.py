@@ -197,3 +197,22 @@ def test_peer_exchange_wait_runs_out_without_hanging():
     ex2[1].wait_merge(out)
     ex2[1].check_status()
     assert_close(out, orc.attention(Q, K, V), torch.float16, what="after timeout")
+
+
+@pytest.mark.parametrize("heads", [(64, 1), (64, 2), (40, 1)], ids=lambda h: f"{h[0]}q{h[1]}kv")
+@pytest.mark.parametrize("D", [64, 128])
+def test_large_group_decode_ignores_cache_tail(heads, D):
+    """More than 16 query heads per KV head run on the tcgen05 kernel (the heads of a group are the
+    rows of one query tile).  The cache past each sequence's valid length is filled with NaN: it
+    must not reach the result, whichever split it falls into."""
+    Hq, Hkv = heads
+    B, L, dtype = 5, 3000, torch.bfloat16
+    Q, K, V = qkv(2100 + Hq + D, B, Hq, Hkv, 1, L, D, dtype)
+    lens = torch.tensor([1, 127, 128, 1501, 3000], dtype=torch.int32)
+    Kd, Vd = K.to(DEV), V.to(DEV)
+    for b in range(B):
+        Kd[b, :, int(lens[b]):] = float("nan")
+        Vd[b, :, int(lens[b]):] = float("nan")
+    got = dense(Q.to(DEV), Kd, Vd, kv_lens=lens.to(DEV))
+    assert torch.isfinite(got).all()
+    assert_close(got, orc.attention(Q, K, V, kv_lens=lens), dtype, what=f"large-group decode {heads} D={D}")
