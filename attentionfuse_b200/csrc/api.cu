@@ -142,19 +142,31 @@ int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32_t H_q,
 }
 
 int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count) {
-  // One CTA per (split, batch, kv head), two CTAs resident per SM.  Bandwidth-bound groups
-  // (<= 16 query heads per KV head) want about five waves of CTAs so that the ragged tail of
-  // per-sequence lengths averages out; the tensor-bound MQA case wants one wave.  Keep at least
-  // 512 keys per split so the pipeline prologue amortises; cap at 64.
+  // Bandwidth-bound groups (<= 16 query heads per KV head): one CTA per (split, batch, kv head),
+  // two CTAs resident per SM, about five waves of CTAs so that the ragged tail of per-sequence
+  // lengths averages out.  Keep at least 512 keys per split so the pipeline prologue amortises;
+  // cap at 64.
   if (sm_count <= 0) sm_count = 148;
   if (B < 1) B = 1;
   if (H_kv < 1) H_kv = 1;
   const int group = H_q > H_kv ? H_q / H_kv : 1;
   const int64_t units = (int64_t)B * H_kv * ((group + 63) / 64);
-  const int64_t slots = 2LL * sm_count * (group > 16 ? 1 : 5);
-  // one wave must fit the resident slots (round down: one CTA too many doubles the time);
-  // several waves round up
-  int64_t want = group > 16 ? slots / units : (slots + units - 1) / units;
+  int64_t want;
+  if (group > 16) {
+    // Tensor-bound groups run on the persistent tcgen05 kernel, one CTA per SM: long items
+    // amortise the per-item prologue and epilogue, so aim at one or two items per CTA, whichever
+    // fills the SMs better (never one item more than a whole number of rounds).
+    const int64_t s1 = sm_count / units > 0 ? sm_count / units : 1;
+    const int64_t s2 = 2LL * sm_count / units > 0 ? 2LL * sm_count / units : 1;
+    auto fill = [&](int64_t s) {
+      const int64_t items = units * s, rounds = (items + sm_count - 1) / sm_count;
+      return (double)items / (double)(rounds * sm_count);
+    };
+    want = fill(s2) > fill(s1) + 1e-9 ? s2 : s1;
+  } else {
+    const int64_t slots = 2LL * sm_count * 5;
+    want = (slots + units - 1) / units;
+  }
   const int64_t cap = N_kv / 512 > 1 ? N_kv / 512 : 1;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
