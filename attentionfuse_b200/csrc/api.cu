@@ -37,6 +37,7 @@ int validate_problem(const AfProblem& p) {
   AF_REQUIRE(p.norm_kind == AF_NORM_SOFTMAX || p.norm_kind == AF_NORM_RELU, "unknown norm_kind %d", p.norm_kind);
   AF_REQUIRE(p.q && p.k && p.v, "q/k/v must be non-NULL");
   AF_REQUIRE((int64_t)p.B * p.H_q <= 65535, "B*H_q exceeds the launch grid limit");
+  AF_REQUIRE(p.q_offset >= 0, "q_offset must be non-negative (got %d)", p.q_offset);
   if (p.mask_kind == AF_MASK_WINDOW) AF_REQUIRE(p.window > 0, "window must be positive");
   if (p.mask_kind == AF_MASK_BLOCKS) {
     AF_REQUIRE(p.block_m > 0 && p.block_n > 0, "block sizes must be positive");
@@ -88,6 +89,7 @@ int af_bwd(const AfBwdParams* params, af_stream_t stream) {
   int rc = validate_problem(a.p);
   if (rc != AF_OK) return rc;
   AF_REQUIRE(a.p.norm_kind == AF_NORM_SOFTMAX, "backward is defined for softmax normalisation only");
+  AF_REQUIRE(a.p.q_offset == 0, "backward does not take a query position offset");
   AF_REQUIRE(a.o && a.d_o && a.lse && a.delta && a.dq && a.dk && a.dv, "NULL backward operand");
   if (a.p.mask_kind == AF_MASK_BLOCKS) AF_REQUIRE(a.p.q_num && a.p.q_idx, "backward needs key-major block lists");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
   }
   __syncthreads();
   if (p.rope) {
-    rope_tile<T, LD>(sQ, TM, r0, r_end, D, p.cos, p.sin, p.rope_stride_n);
+    rope_tile<T, LD>(sQ, TM, r0 + p.q_offset, r_end + p.q_offset, D, p.cos, p.sin, p.rope_stride_n);
     __syncthreads();
   }
 
@@ -136,21 +136,22 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = r0 + ty * 4 + i;
+      const int pos = row + p.q_offset;          // the row's position on the key axis
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int key = k0 + tx + 16 * j;
         float x = s[i][j] * p.sm_scale;
         if (p.bias_kind == AF_BIAS_ALIBI) {
-          x += -slope * (float)abs(row - key);
+          x += -slope * (float)abs(pos - key);
         } else if (p.bias_kind == AF_BIAS_ADDITIVE) {
           if (row < p.N_q && key < p.N_kv)
             x += ld_elem<T>(p.bias, (int64_t)b * p.bias_stride[0] + (int64_t)h * p.bias_stride[1] +
                                         (int64_t)row * p.bias_stride[2] + (int64_t)key * p.bias_stride[3]);
         }
         bool keep = key < k_end;
-        if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (row >= key);
-        if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(row - key) < p.window);
+        if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (pos >= key);
+        if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(pos - key) < p.window);
         x = keep ? x : -INFINITY;
         s[i][j] = x;
         mx = fmaxf(mx, x);
@@ -215,10 +216,10 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
     }
   } else {
     int lo = 0, hi = p.N_kv;
-    if (p.mask_kind == AF_MASK_CAUSAL) hi = min(hi, r_end);
+    if (p.mask_kind == AF_MASK_CAUSAL) hi = min(hi, r_end + p.q_offset);
     if (p.mask_kind == AF_MASK_WINDOW) {
-      lo = max(0, r0 - p.window + 1);
-      hi = min(hi, r_end + p.window - 1);
+      lo = max(0, r0 + p.q_offset - p.window + 1);
+      hi = min(hi, r_end + p.q_offset + p.window - 1);
     }
     for (int k0 = lo; k0 < hi; k0 += TN) process(k0, min(k0 + TN, hi));
   }

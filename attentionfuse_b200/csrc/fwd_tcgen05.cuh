@@ -127,8 +127,8 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   // the diagonal sets the reference in the first tile and every later tile stays below it.
   w.step = (p.mask_kind == AF_MASK_CAUSAL && p.bias_kind == AF_BIAS_ALIBI) ? -1 : 1;
   w.n_kv = p.N_kv;
-  const int m0 = m_blk * BM;
-  const int m_end = min(m0 + BM, p.N_q);
+  const int m0 = m_blk * BM + p.q_offset;                 // first / one-past-last position of the tile
+  const int m_end = min(m_blk * BM + BM, p.N_q) + p.q_offset;
   if (p.mask_kind == AF_MASK_BLOCKS) {
     const int qb = m_blk / args.q_tiles_per_block;
     w.per_block = args.kv_tiles_per_block;
@@ -542,8 +542,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       if (ROPE != ROPE_NONE && n_tiles > 0 && half == 0) {
         if (mbar_wait(&bars->q_full, qi & 1, abort_flag)) {
           if (row < p.N_q)
-            rope_row<T, D>(sQ, rtid, reinterpret_cast<const T*>(p.cos) + (int64_t)row * p.rope_stride_n,
-                           reinterpret_cast<const T*>(p.sin) + (int64_t)row * p.rope_stride_n);
+            rope_row<T, D>(sQ, rtid, reinterpret_cast<const T*>(p.cos) + (int64_t)(row + p.q_offset) * p.rope_stride_n,
+                           reinterpret_cast<const T*>(p.sin) + (int64_t)(row + p.q_offset) * p.rope_stride_n);
           fence_proxy_async_smem();
           mbar_arrive(&bars->q_ready);
         }
@@ -566,11 +566,12 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 
         // Tile-level decision: only edge / diagonal tiles pay for element masking.
         bool need_mask = key0 + BN > walk.n_kv;
-        if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > m0);
+        const int pos0 = m0 + p.q_offset;           // position of the tile's first row on the key axis
+        if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > pos0);
         if (EMASK == EMASK_WINDOW)
-          need_mask = need_mask || (m0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - m0 >= p.window);
+          need_mask = need_mask || (pos0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - pos0 >= p.window);
         const int col0 = key0 + half * HALF_COLS;   // key index of this thread's column 0
-        const int rel = row - col0;                 // column c is kept iff ...
+        const int rel = row + p.q_offset - col0;    // column c is kept iff ...
         if (need_mask) {
           const int kmax = walk.n_kv - col0;        // ... c < kmax
 #pragma unroll

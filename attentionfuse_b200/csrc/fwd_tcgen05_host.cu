@@ -64,6 +64,7 @@ struct RotateJob {
   const void* src; void* dst;   // dst == nullptr: nothing to do
   int64_t s0, s1, s2;
   int H, N;
+  int pos0;                     // position of row 0 in the cos / sin tables
 };
 
 template <typename T>
@@ -126,18 +127,23 @@ __global__ void rope_prepass_kernel(const RotateJob jq, const RotateJob jk, cons
   const int n = blockIdx.x * (blockDim.x / HC) + threadIdx.x / HC;
   const int64_t b = blockIdx.y;
   if (n >= n_max) return;
-  const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + c * 8));
-  const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)n * sr + D / 2 + c * 8));
-  const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + c * 8));
-  const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)n * sr + D / 2 + c * 8));
-  rotate_heads<T, D>(jq, b, n, c, cl, ch, sl, sh);
+  auto load = [&](int pos, uint4& cl, uint4& ch, uint4& sl, uint4& sh) {
+    cl = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)pos * sr + c * 8));
+    ch = __ldg(reinterpret_cast<const uint4*>(cos_ + (int64_t)pos * sr + D / 2 + c * 8));
+    sl = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)pos * sr + c * 8));
+    sh = __ldg(reinterpret_cast<const uint4*>(sin_ + (int64_t)pos * sr + D / 2 + c * 8));
+  };
+  uint4 cl, ch, sl, sh;
+  if (n < jk.N || jq.pos0 == 0) load(n, cl, ch, sl, sh);
   rotate_heads<T, D>(jk, b, n, c, cl, ch, sl, sh);
+  if (jq.pos0 != 0 && jq.dst != nullptr && n < jq.N) load(n + jq.pos0, cl, ch, sl, sh);   // queries sit further along
+  rotate_heads<T, D>(jq, b, n, c, cl, ch, sl, sh);
 }
 
 template <typename T, int D>
 int launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st) {
-  RotateJob jq{p.q, q_out, p.q_stride[0], p.q_stride[1], p.q_stride[2], p.H_q, p.N_q};
-  RotateJob jk{p.k, k_out, p.k_stride[0], p.k_stride[1], p.k_stride[2], p.H_kv, p.N_kv};
+  RotateJob jq{p.q, q_out, p.q_stride[0], p.q_stride[1], p.q_stride[2], p.H_q, p.N_q, p.q_offset};
+  RotateJob jk{p.k, k_out, p.k_stride[0], p.k_stride[1], p.k_stride[2], p.H_kv, p.N_kv, 0};
   const int n_max = p.N_q > p.N_kv ? p.N_q : p.N_kv;
   constexpr int THREADS = 128, ROWS = THREADS / (D / 16);
   AF_REQUIRE(p.B <= 65535, "batch exceeds the launch grid limit");

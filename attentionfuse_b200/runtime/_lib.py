@@ -42,6 +42,7 @@ class AfProblem(C.Structure):
         ("q_num", PTR), ("q_idx", PTR),
         ("q_num_stride_h", I64), ("q_idx_stride_h", I64), ("q_idx_stride_k", I64),
         ("status", PTR),
+        ("q_offset", I32),
     ]
 
 

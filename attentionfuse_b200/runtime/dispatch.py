@@ -50,7 +50,8 @@ def _rope_table(t: torch.Tensor, name: str, like: torch.Tensor) -> torch.Tensor:
 
 
 def fill_problem(p: _lib.AfProblem, Q, K, V, *, sm_scale, mask_kind, window=0, bias_kind=0,
-                 norm_kind=0, slopes=None, bias=None, cos=None, sin=None, family=None, keep=None):
+                 norm_kind=0, slopes=None, bias=None, cos=None, sin=None, family=None, keep=None,
+                 q_offset=0):
     """Fill the shape / operand part of a parameter block.  `keep` collects tensors that must
     outlive the launch call (temporaries made contiguous here)."""
     B, H_q, N_q, D = Q.shape
@@ -61,6 +62,7 @@ def fill_problem(p: _lib.AfProblem, Q, K, V, *, sm_scale, mask_kind, window=0, b
     p.family = family
     p.B, p.H_q, p.H_kv, p.N_q, p.N_kv, p.D = B, H_q, H_kv, N_q, N_kv, D
     p.sm_scale = float(sm_scale)
+    p.q_offset = int(q_offset)
     p.mask_kind, p.window, p.bias_kind, p.norm_kind = mask_kind, int(window or 0), bias_kind, norm_kind
     p.q, p.q_stride = Q.data_ptr(), _lib.strides(Q)
     p.k, p.k_stride = K.data_ptr(), _lib.strides(K)
@@ -96,14 +98,14 @@ def validate_qkv(Q, K, V):
 
 def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, norm_kind=0,
                    slopes=None, bias=None, cos=None, sin=None, save_lse=None,
-                   block_lists=None, family=None):
+                   block_lists=None, family=None, q_offset=0):
     """Fill AfFwdParams and call af_fwd on the current stream."""
     lib = _lib.load()
     params = _lib.AfFwdParams()
     keep: list = []
     fill_problem(params.p, Q, K, V, sm_scale=sm_scale, mask_kind=mask_kind, window=window,
                  bias_kind=bias_kind, norm_kind=norm_kind, slopes=slopes, bias=bias,
-                 cos=cos, sin=sin, family=family, keep=keep)
+                 cos=cos, sin=sin, family=family, keep=keep, q_offset=q_offset)
     if block_lists is not None:
         block_lists.fill(params.p, Q.shape[1])
     params.o, params.o_stride = out.data_ptr(), _lib.strides(out)
@@ -123,19 +125,25 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
                   bias: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
                   sin: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                   save_lse: Optional[torch.Tensor] = None, *, alibi_slopes=None,
-                  kv_lens: Optional[torch.Tensor] = None, family: Optional[int] = None) -> torch.Tensor:
+                  kv_lens: Optional[torch.Tensor] = None, family: Optional[int] = None,
+                  q_offset: Optional[int] = None) -> torch.Tensor:
     """Run the fused forward; returns O with Q's shape and dtype.
 
     Extensions over the reference signature (all keyword-only): ``alibi_slopes`` overrides the
     default slope table of an ALiBi graph; ``kv_lens`` (int32 [B]) gives per-sequence valid
-    cache lengths for query-length-1 decoding; ``family`` forces a kernel family.
+    cache lengths for query-length-1 decoding; ``family`` forces a kernel family; ``q_offset``
+    places query row 0 at that position of the key axis (chunked prefill against a cache: row
+    i is masked, biased and rotated as position ``q_offset + i``), which also lifts the
+    reference's restriction of masked graphs to N_q == N_kv (attnfuse/runtime/dispatch.py:140-148).
     """
     validate_qkv(Q, K, V)
     N_q, N_kv = Q.shape[2], K.shape[2]
     bundle = get_or_compile(graph)
+    if q_offset is not None and (not isinstance(q_offset, int) or q_offset < 0):
+        raise ValueError(f"q_offset must be a non-negative int; got {q_offset!r}")
 
     from .flash_decode import can_use_flash_decode, run_flash_decode
-    if save_lse is None and can_use_flash_decode(graph, Q, K):
+    if save_lse is None and not q_offset and can_use_flash_decode(graph, Q, K):
         if out is None:
             out = torch.empty_like(Q)
         return run_flash_decode(graph, Q, K, V, bundle.sm_scale, bundle.bias_kind, K.shape[1], out,
@@ -144,7 +152,7 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
         raise ValueError("kv_lens is only supported on the flash-decoding path "
                          "(query length 1, f16/bf16, head_dim 64/128, N_kv >= 256)")
 
-    if N_q != N_kv:
+    if N_q != N_kv and q_offset is None:
         kinds = {m.kind for m in graph.collect_masks()}
         if kinds - {MaskKind.FULL}:
             raise ValueError(
@@ -176,11 +184,11 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
                 "This attention graph was built with af.rope(); you must pass cos=<table> "
                 "and sin=<table> at call time.")
         c, s = _rope_table(cos, "cos", Q), _rope_table(sin, "sin", Q)
-        if c.shape[0] < max(N_q, N_kv) or c.shape[1] != Q.shape[3] or s.shape != c.shape:
-            raise ValueError(f"cos/sin tables must be (>= {max(N_q, N_kv)}, {Q.shape[3]}); "
+        if c.shape[0] < max(N_q + (q_offset or 0), N_kv) or c.shape[1] != Q.shape[3] or s.shape != c.shape:
+            raise ValueError(f"cos/sin tables must be (>= {max(N_q + (q_offset or 0), N_kv)}, {Q.shape[3]}); "
                              f"got {tuple(c.shape)}, {tuple(s.shape)}")
 
     return launch_forward(Q, K, V, out, sm_scale=bundle.sm_scale, mask_kind=bundle.mask_kind,
                           window=bundle.window, bias_kind=bundle.bias_kind,
                           norm_kind=bundle.norm_kind, slopes=slopes, bias=bias, cos=c, sin=s,
-                          save_lse=save_lse, family=family)
+                          save_lse=save_lse, family=family, q_offset=q_offset or 0)

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define AF_ABI_VERSION 1
+#define AF_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define AF_API __attribute__((visibility("default")))
@@ -81,6 +81,11 @@ typedef struct AfProblem {
   const int32_t* q_num; const int32_t* q_idx;
   int64_t q_num_stride_h, q_idx_stride_h, q_idx_stride_k;
   int32_t* status;    /* optional device word, AF_STATUS_*; may be NULL                     */
+  int32_t q_offset;   /* position of query row 0 on the key axis (chunked prefill against a
+                         cache): row i is masked, biased and rotated as position q_offset + i.
+                         Forward only; no counterpart in the reference, whose kernels index
+                         rows and columns from 0 (attnfuse/compiler/codegen.py:126-135,216-217)
+                         and reject masks when N_q != N_kv (attnfuse/runtime/dispatch.py:140-148) */
 } AfProblem;
 
 typedef struct AfFwdParams {

@@ -63,7 +63,7 @@ def expand_kv(t: torch.Tensor, group: int) -> torch.Tensor:
 
 
 def scores(Q, K, *, scale=None, causal=False, window=None, slopes=None, bias=None,
-           elem_mask=None, kv_lens=None, q_positions=None) -> torch.Tensor:
+           elem_mask=None, kv_lens=None, q_positions=None, q_offset=0) -> torch.Tensor:
     """Masked, biased score matrix (B, H, N_q, N_kv) in Q's dtype.
 
     Follows attnfuse/reference/pytorch_naive.py:22-40 (scale, ALiBi as -slope*|i-j|, causal
@@ -71,11 +71,13 @@ def scores(Q, K, *, scale=None, causal=False, window=None, slopes=None, bias=Non
     (attnfuse/compiler/codegen.py:347-352), an element mask (tests/test_block_sparse.py:35-40)
     and per-sequence valid lengths for decoding.  `q_positions` (B,) overrides the query
     position used by ALiBi when N_q == 1 (attnfuse/compiler/codegen_decode.py:142-145 measures
-    the distance from the last key)."""
+    the distance from the last key).  `q_offset` places query row 0 at that position of the key
+    axis (chunked prefill against a cache; an extension with no counterpart in the reference,
+    defined so that the rows agree with the same rows of the full square problem)."""
     B, H, N_q, D = Q.shape
     N_kv = K.shape[2]
     s = torch.matmul(Q, K.transpose(-2, -1)) * (scale if scale is not None else 1.0 / math.sqrt(D))
-    qi = torch.arange(N_q)
+    qi = torch.arange(N_q) + q_offset
     kj = torch.arange(N_kv)
     rel = qi[:, None] - kj[None, :]
     if slopes is not None:
@@ -102,7 +104,7 @@ def scores(Q, K, *, scale=None, causal=False, window=None, slopes=None, bias=Non
 
 def attention(Q, K, V, *, scale=None, causal=False, window=None, slopes=None, bias=None,
               cos=None, sin=None, elem_mask=None, kv_lens=None, q_positions=None,
-              relu=False, return_lse=False, dtype=torch.float32):
+              relu=False, return_lse=False, dtype=torch.float32, q_offset=0):
     """Full attention in `dtype` with GQA expansion and optional RoPE pre-rotation.
 
     RoPE: rotate in `dtype`, round the rotated Q, K back to the input dtype, as the reference
@@ -115,13 +117,13 @@ def attention(Q, K, V, *, scale=None, causal=False, window=None, slopes=None, bi
     q, k, v = Q.to(dtype), K.to(dtype), V.to(dtype)
     if cos is not None:
         c, s_ = cos.to(dtype), sin.to(dtype)
-        q = apply_rope(q, c[: q.shape[2]], s_[: q.shape[2]]).to(in_dtype).to(dtype)
+        q = apply_rope(q, c[q_offset: q_offset + q.shape[2]], s_[q_offset: q_offset + q.shape[2]]).to(in_dtype).to(dtype)
         k = apply_rope(k, c[: k.shape[2]], s_[: k.shape[2]]).to(in_dtype).to(dtype)
     if group > 1:
         k, v = expand_kv(k, group), expand_kv(v, group)
     s = scores(q, k, scale=scale, causal=causal, window=window,
                slopes=None if slopes is None else slopes.to(dtype), bias=bias,
-               elem_mask=elem_mask, kv_lens=kv_lens, q_positions=q_positions)
+               elem_mask=elem_mask, kv_lens=kv_lens, q_positions=q_positions, q_offset=q_offset)
     if relu:
         # ReLU normalisation: max(s, 0) divided by its row sum (attnfuse/compiler/codegen.py:364-374)
         p = torch.clamp(s, min=0.0)

@@ -116,3 +116,16 @@ def test_cfg1_matches_reference():
     out = orc.attention(Q, K, V, causal=True, cos=cos, sin=sin, slopes=g["slopes"])
     close(out[:, :, ::37, :], g["out_sample"], 5e-6)
     assert abs(out.double().sum().item() - g["out_sum"].item()) < 1e-2
+
+
+def test_query_offset_rows_are_rows_of_the_square_problem():
+    """`q_offset` (chunked prefill against a cache) is defined by this property."""
+    from tests._util import qkv
+    B, H, N, D, off, n = 1, 3, 96, 16, 40, 30
+    Q, K, V = qkv(77, B, H, H, N, N, D, torch.float32)
+    cos, sin = orc.build_rope_cache(N, D, 10000.0, torch.float32)
+    for kw in (dict(causal=True), dict(window=17), dict(causal=True, slopes=orc.alibi_slopes(H).float()),
+               dict(causal=True, cos=cos, sin=sin)):
+        full = orc.attention(Q, K, V, **kw)
+        part = orc.attention(Q[:, :, off:off + n], K, V, q_offset=off, **kw)
+        assert (full[:, :, off:off + n] - part).abs().max().item() < 1e-6
