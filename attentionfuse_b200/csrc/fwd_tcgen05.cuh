@@ -106,7 +106,6 @@ struct TcArgs {
 // Which key tiles a query tile visits.
 struct TileWalk {
   int n_tiles;
-  int n_kv;                  // keys of this item's sequence (split mode: the batch entry's valid length)
   int first_tile;            // dense / causal / window: lowest tile index
   int step;                  // +1, or -1 when the tiles are walked from the diagonal down
   const int32_t* list;       // block lists: active key blocks of this query block
@@ -126,7 +125,6 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   // would raise the row maximum (and rescale the accumulator) at every tile; walking down from
   // the diagonal sets the reference in the first tile and every later tile stays below it.
   w.step = (p.mask_kind == AF_MASK_CAUSAL && p.bias_kind == AF_BIAS_ALIBI) ? -1 : 1;
-  w.n_kv = p.N_kv;
   const int m0 = m_blk * BM + p.q_offset;                 // first / one-past-last position of the tile
   const int m_end = min(m_blk * BM + BM, p.N_q) + p.q_offset;
   if (p.mask_kind == AF_MASK_BLOCKS) {
@@ -151,7 +149,7 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
 // One work item = one 128-row query tile of one (batch, query head).
 struct Item {
   int m0, b, h, h_kv;
-  int split;                 // split mode: which share of the keys
+  int split, n_kv;           // split mode: which share of the keys; valid keys of the batch entry
   TileWalk walk;
 };
 
@@ -159,7 +157,7 @@ struct Item {
 // r*G + c in even rounds r and r*G + (G-1-c) in odd rounds (c = blockIdx.x, G = gridDim.x): with
 // item weights that fall monotonically the zig-zag evens out the key tiles per CTA to within a
 // fraction of a percent.  With G = number of items every CTA runs exactly one item.
-template <int EMASK>
+template <int EMASK, bool SPLIT>
 __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it) {
   const int G = (int)gridDim.x, c = (int)blockIdx.x;
   const int64_t w64 = (int64_t)round * G + ((round & 1) ? G - 1 - c : c);
@@ -172,15 +170,16 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
   it.h = bh % p.H_q;
   it.h_kv = it.h / (p.H_q / p.H_kv);
   it.split = 0;
-  if (args.num_splits > 0) {
+  it.n_kv = p.N_kv;
+  if (SPLIT) {
     // split-K decode: one query tile per (batch, pseudo-head); the 128-key tiles of the valid
     // length are dealt out evenly to the splits
     it.split = w / bh_count;
     it.m0 = 0;
     TileWalk& wk = it.walk;
     wk.list = nullptr; wk.per_block = 1; wk.step = 1;
-    wk.n_kv = args.kv_lens ? min(max(args.kv_lens[it.b], 0), p.N_kv) : p.N_kv;
-    const int tiles = (wk.n_kv + BN - 1) / BN;
+    it.n_kv = args.kv_lens ? min(max(args.kv_lens[it.b], 0), p.N_kv) : p.N_kv;
+    const int tiles = (it.n_kv + BN - 1) / BN;
     wk.first_tile = (int)((int64_t)it.split * tiles / args.num_splits);
     wk.n_tiles = (int)((int64_t)(it.split + 1) * tiles / args.num_splits) - wk.first_tile;
     return true;
@@ -337,7 +336,7 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk
 // One instantiation per composition: element type, head_dim, RoPE mode, element-level mask and
 // ALiBi are compile-time, so the per-element code of the softmax group carries no run-time
 // branches on the composition.
-template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
+template <typename T, int D, int ROPE, int EMASK, bool ALIBI, bool SPLIT>
 __global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 384 : 352, 1)
 fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
@@ -407,7 +406,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       Item it;
       int g = 0, qi = 0;
       bool ok = true;
-      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+      for (int round = 0; ok && get_item<EMASK, SPLIT>(args, round, it); ++round) {
         const int n_tiles = it.walk.n_tiles;
         if (n_tiles == 0) continue;
         // the single Q buffer is free once the last S product of the previous item has run
@@ -449,7 +448,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       Item it;
       int g = 0, qi = 0;
       bool ok = true;
-      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+      for (int round = 0; ok && get_item<EMASK, SPLIT>(args, round, it); ++round) {
         const int n_tiles = it.walk.n_tiles;
         if (n_tiles == 0) continue;
         ok = mbar_wait(ROPE != ROPE_NONE ? &bars->q_ready : &bars->q_full, qi & 1, abort_flag);
@@ -485,7 +484,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       Item it;
       int g = 0, qi = 0;
       bool ok = true;
-      for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+      for (int round = 0; ok && get_item<EMASK, SPLIT>(args, round, it); ++round) {
         const int n_tiles = it.walk.n_tiles;
         if (n_tiles == 0) continue;
         for (int j = 0; j < n_tiles; ++j) {
@@ -534,7 +533,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     int g = 0, qi = 0;
     uint32_t pair_count = 0;
     bool alive = true;
-    for (int round = 0; alive && get_item<EMASK>(args, round, it); ++round) {
+    for (int round = 0; alive && get_item<EMASK, SPLIT>(args, round, it); ++round) {
       const TileWalk& walk = it.walk;
       const int n_tiles = walk.n_tiles;
       const int m0 = it.m0, b = it.b, h = it.h;
@@ -565,7 +564,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         tmem_wait_ld();
 
         // Tile-level decision: only edge / diagonal tiles pay for element masking.
-        bool need_mask = key0 + BN > walk.n_kv;
+        const int n_kv = SPLIT ? it.n_kv : p.N_kv;
+        bool need_mask = key0 + BN > n_kv;
         const int pos0 = m0 + p.q_offset;           // position of the tile's first row on the key axis
         if (EMASK == EMASK_CAUSAL) need_mask = need_mask || (key0 + BN - 1 > pos0);
         if (EMASK == EMASK_WINDOW)
@@ -573,7 +573,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         const int col0 = key0 + half * HALF_COLS;   // key index of this thread's column 0
         const int rel = row + p.q_offset - col0;    // column c is kept iff ...
         if (need_mask) {
-          const int kmax = walk.n_kv - col0;        // ... c < kmax
+          const int kmax = n_kv - col0;             // ... c < kmax
 #pragma unroll
           for (int c = 0; c < HALF_COLS; ++c) {
             bool keep = c < kmax;
@@ -641,14 +641,14 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           exp_pass<T, ALIBI ? EXP_PRESCALED : EXP_SCALE>(xr, pk, scale2, neg_m, 0.f, rsum);
         }
         l_part = l_part * alpha + rsum;
-        if (args.num_splits > 0 && key0 + BN > walk.n_kv) {
+        if (SPLIT && key0 + BN > n_kv) {
           // Split-K decode: cache rows past the valid length hold whatever the allocation held
           // (TMA zero-fills only past the tensor's extent) and 0 * NaN would poison O, so the
           // softmax threads clear those V rows of the stage before they release P.
           const int s = gg % STAGES;
           if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { alive = false; break; }
           // each half clears the rows its own P.V product reads (keys [64 half, 64 half + 64))
-          const int first = max(walk.n_kv - key0, half * HALF_COLS), last = (half + 1) * HALF_COLS;
+          const int first = max(n_kv - key0, half * HALF_COLS), last = (half + 1) * HALF_COLS;
           const uint32_t v_tile = sV0 + s * C::TILE_BYTES;
           for (int idx = rtid; idx < (last - first) * C::PANELS * 8; idx += BM) {
             const int r = first + idx / (C::PANELS * 8), rem = idx % (C::PANELS * 8);
@@ -702,7 +702,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
       }
-      if (args.num_splits > 0) {
+      if (SPLIT) {
         // split-K decode: un-normalised partial of this (split, batch, head) for the combine kernel
         if (row < p.N_q) {
           const int64_t wr = ((int64_t)it.split * p.B + b) * ((int64_t)p.H_q * p.N_q) + (int64_t)h * p.N_q + row;
@@ -746,7 +746,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
     Item it;
     int g = 0;
     bool ok = true;
-    for (int round = 0; ok && get_item<EMASK>(args, round, it); ++round) {
+    for (int round = 0; ok && get_item<EMASK, SPLIT>(args, round, it); ++round) {
       const int n_tiles = it.walk.n_tiles;
       for (int j = 0; j < n_tiles; ++j) {
         const int gg = g + j;
@@ -781,10 +781,10 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 // ---------------------------------------------------------------------------------------
 // Launch of one instantiation (tensor maps are encoded by the host file)
 // ---------------------------------------------------------------------------------------
-template <typename T, int D, int ROPE, int EMASK, bool ALIBI>
+template <typename T, int D, int ROPE, int EMASK, bool ALIBI, bool SPLIT = false>
 int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                     cudaStream_t st) {
-  auto kern = fwd_tcgen05_kernel<T, D, ROPE, EMASK, ALIBI>;
+  auto kern = fwd_tcgen05_kernel<T, D, ROPE, EMASK, ALIBI, SPLIT>;
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static bool configured = false;   // benign race: the attribute call is idempotent
   if (!configured) {
@@ -802,6 +802,10 @@ template <typename T, int D, int ROPE>
 int launch_composition(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                        cudaStream_t st) {
   const AfProblem& p = args.a.p;
+  if (args.num_splits > 0) {   // split-K decode: dense, no bias, no rotation (one extra instantiation)
+    if constexpr (ROPE == ROPE_NONE) return launch_instance<T, D, ROPE_NONE, EMASK_NONE, false, true>(args, mq, mk, mv, st);
+    else return fail(AF_ERR_UNSUPPORTED, "split-K decode takes no rotation");
+  }
   const int em = p.mask_kind == AF_MASK_CAUSAL ? EMASK_CAUSAL : p.mask_kind == AF_MASK_WINDOW ? EMASK_WINDOW : EMASK_NONE;
   const bool alibi = p.bias_kind == AF_BIAS_ALIBI;
   switch (em * 2 + (alibi ? 1 : 0)) {

@@ -39,7 +39,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload,
 # from the ncu capture summarised under profiles/: the capture ran the same shape at batch 2
 # (traffic grows in proportion to the batch) and is scaled to the batch-4 launch here.
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = 268.4e6   # 134.2 MB captured at batch 2 (profiles/fwd_tcgen05_causal_rope_bf16_d128.md), x2 for batch 4
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = 264.4e6   # 132.2 MB captured at batch 2 (profiles/fwd_tcgen05_causal_rope_bf16_d128.md), x2 for batch 4
 
 
 def peaks():
