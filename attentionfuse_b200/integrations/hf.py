@@ -51,6 +51,24 @@ def _is_pure_causal_mask(mask: Optional[torch.Tensor], N_q: int, N_kv: int) -> b
     return True
 
 
+def _is_chunk_causal_mask(mask: Optional[torch.Tensor], N_q: int, N_kv: int) -> bool:
+    """True iff `mask` looks like the causal triangle of a chunk of N_q queries that sits at the
+    end of a cache of N_kv keys (row i sees keys 0 .. N_kv - N_q + i): three entries of the
+    first row and the last corner are checked, in the spirit of the corner test above."""
+    if mask is None or mask.dim() != 4 or mask.shape[-2] != N_q or mask.shape[-1] != N_kv:
+        return False
+    if not (1 < N_q < N_kv):
+        return False
+    off = N_kv - N_q
+    probe = torch.stack([mask[..., 0, 0], mask[..., 0, off], mask[..., 0, off + 1], mask[..., -1, -1]], dim=-1)
+    if mask.dtype == torch.bool:            # True = attend
+        seen = probe
+    else:
+        seen = probe > torch.finfo(mask.dtype).min / 2
+    want = torch.tensor([True, True, False, True], device=mask.device)
+    return bool((seen == want).all().item())
+
+
 def attnfuse_attention_forward(module: torch.nn.Module, query: torch.Tensor, key: torch.Tensor,
                                value: torch.Tensor, attention_mask: Optional[torch.Tensor],
                                dropout: float = 0.0, scaling: Optional[float] = None,
@@ -58,9 +76,12 @@ def attnfuse_attention_forward(module: torch.nn.Module, query: torch.Tensor, key
     """query (B, H_q, N_q, D), key/value (B, H_kv, N_kv, D); GQA handled by the kernel (no
     repeat_kv).  Returns (attn_output as (B, N_q, H_q, D), None)."""
     N_q, N_kv = query.shape[2], key.shape[2]
-    needs_fallback = dropout > 0.0 or not _is_pure_causal_mask(attention_mask, N_q, N_kv)
-    if attention_mask is not None and N_q != N_kv and N_q > 1:
-        needs_fallback = True   # chunked prefill against a cache needs a position offset
+    wants_grad = torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad)
+    # a chunk of queries at the end of a cache: causal with a position offset (forward only)
+    chunk = dropout == 0.0 and not wants_grad and _is_chunk_causal_mask(attention_mask, N_q, N_kv)
+    needs_fallback = not chunk and (dropout > 0.0 or not _is_pure_causal_mask(attention_mask, N_q, N_kv))
+    if not chunk and attention_mask is not None and N_q != N_kv and N_q > 1:
+        needs_fallback = True
     if needs_fallback:
         from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
         return ALL_ATTENTION_FUNCTIONS["sdpa"](
@@ -69,16 +90,17 @@ def attnfuse_attention_forward(module: torch.nn.Module, query: torch.Tensor, key
 
     if is_causal is None:
         is_causal = getattr(module, "is_causal", True)
-    causal_for_us = bool(is_causal) and N_q > 1 and N_q == N_kv
+    causal_for_us = chunk or (bool(is_causal) and N_q > 1 and N_q == N_kv)
     attn_fn = _get_attn_fn(query.shape[-1], query.dtype, causal_for_us, scaling)
     B, H, _, D = query.shape
-    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+    if wants_grad:
         return attn_fn(query, key, value).transpose(1, 2).contiguous(), None
     # Inference: let the kernel write (B, N, H, D) directly through a transposed view.
     out_bnhd = torch.empty(B, N_q, H, D, dtype=query.dtype, device=query.device)
     from ..runtime.dispatch import run_attention
     graph = attn_fn(query, key, value, return_graph=True)
-    run_attention(graph, query, key, value, out=out_bnhd.transpose(1, 2))
+    run_attention(graph, query, key, value, out=out_bnhd.transpose(1, 2),
+                  q_offset=(N_kv - N_q) if chunk else None)
     return out_bnhd, None
 
 

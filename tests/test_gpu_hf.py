@@ -80,3 +80,27 @@ def test_cached_decode_step_matches_sdpa():
             step = model(ids[:, -1:], past_key_values=pre.past_key_values, use_cache=True)
             outs[name] = step.logits.float()
     assert (outs["sdpa"] - outs["attnfuse"]).abs().max().item() < 3e-2
+
+
+def test_chunked_prefill_against_cache_stays_on_the_kernel(monkeypatch):
+    """A chunk of queries at the end of a longer cache, with HF's additive causal mask: served by
+    the kernel with a position offset, not by the SDPA fall-back."""
+    import attentionfuse_b200.integrations.hf as hf
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+    from oracle import attention_oracle as orc
+    from tests._util import assert_close, qkv
+    B, Hq, Hkv, N_q, N_kv, D = 2, 4, 2, 100, 300, 64
+    Q, K, V = qkv(4100, B, Hq, Hkv, N_q, N_kv, D, torch.bfloat16)
+    off = N_kv - N_q
+    i = torch.arange(N_q).view(N_q, 1) + off
+    j = torch.arange(N_kv).view(1, N_kv)
+    mask = torch.zeros(B, 1, N_q, N_kv, dtype=torch.bfloat16)
+    mask.masked_fill_((j > i).view(1, 1, N_q, N_kv), torch.finfo(torch.bfloat16).min)
+
+    def no_fallback(*a, **k):
+        raise AssertionError("fell back to SDPA")
+    monkeypatch.setitem(ALL_ATTENTION_FUNCTIONS, "sdpa", no_fallback)
+    out, _ = hf.attnfuse_attention_forward(torch.nn.Identity(), Q.to(DEV), K.to(DEV), V.to(DEV), mask.to(DEV),
+                                           is_causal=False)
+    want = orc.attention(Q, K, V, causal=True, q_offset=off)
+    assert_close(out.transpose(1, 2), want, torch.bfloat16, what="HF chunked prefill")
