@@ -15,7 +15,7 @@ bool bwd_mma_supports(const AfBwdParams& a, const char** why) {
   if (p.D != 64 && p.D != 128) return no("head_dim is not 64 or 128");
   if (p.norm_kind != AF_NORM_SOFTMAX) return no("normalisation is not softmax");
   if (p.bias_kind == AF_BIAS_ADDITIVE) return no("additive bias");
-  if (p.mask_kind == AF_MASK_WINDOW) return no("sliding window");
+  if (p.mask_kind == AF_MASK_WINDOW && p.window < 1) return no("window must be positive");
   if (!(p.sm_scale > 0.f)) return no("non-positive scale");
   if (p.N_q < 1 || p.N_kv < 1) return no("empty sequence");
   if (p.mask_kind == AF_MASK_CAUSAL && p.N_q != p.N_kv) return no("causal with N_q != N_kv");

@@ -34,7 +34,7 @@ using tc::Pack2;
 using tc::ex2_approx;
 
 enum { MODE_DKV = 0, MODE_DQ = 1 };
-enum { EMASK_NONE = 0, EMASK_CAUSAL = 1 };
+enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };   // element-level mask of the instantiation
 
 constexpr int BS = 128;   // rows of the stationary operands (TMEM lanes)
 constexpr int BT = 64;    // rows of a streamed tile (columns of S per step)
@@ -98,6 +98,12 @@ __device__ __forceinline__ StepWalk make_steps(const AfProblem& p, const BwdArgs
       w.list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)blk * p.kv_idx_stride_q;
       w.cnt = p.kv_num[(int64_t)h * p.kv_num_stride_h + blk] * w.per;
     }
+  } else if (p.mask_kind == AF_MASK_WINDOW) {
+    // rows of the streamed operand within |i - j| < window of the stationary tile [t0, t0 + BS)
+    const int n_strm = (MODE == MODE_DKV) ? p.N_q : p.N_kv;
+    const int lo = max(0, t0 - p.window + 1), hi = min(n_strm, t0 + BS + p.window - 1);
+    w.first = lo / BT;
+    w.cnt = hi > lo ? (hi + BT - 1) / BT - w.first : 0;
   } else if (MODE == MODE_DKV) {
     const int total = (p.N_q + BT - 1) / BT;
     w.first = (p.mask_kind == AF_MASK_CAUSAL) ? t0 / BT : 0;     // query rows >= first key of the tile
@@ -334,6 +340,8 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         bool need_mask = col_limit < BT;
         if (EMASK == EMASK_CAUSAL)
           need_mask = need_mask || ((MODE == MODE_DKV) ? (r0 < t0 + BS - 1) : (r0 + BT - 1 > t0));
+        if (EMASK == EMASK_WINDOW)
+          need_mask = need_mask || (r0 + BT - 1 - t0 >= p.window) || (t0 + BS - 1 - r0 >= p.window);
         const int rel = srow - r0;   // DKV: query c kept iff c >= rel;  DQ: key c kept iff c <= rel
 
         uint32_t pk[BT / 2], dk[BT / 2];
@@ -364,6 +372,7 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
               if (MASKED) {
                 bool keep = cc < col_limit;
                 if (EMASK == EMASK_CAUSAL) keep = keep && ((MODE == MODE_DKV) ? (cc >= rel) : (cc <= rel));
+                if (EMASK == EMASK_WINDOW) keep = keep && (cc - rel < p.window) && (rel - cc < p.window);
                 pr = keep ? pr : 0.f;
               }
               pe[u] = pr;
@@ -518,8 +527,13 @@ template <typename T, int D, int MODE>
 int launch_composition(const BwdArgs& args, const CUtensorMap& a1, const CUtensorMap& a2, const CUtensorMap& b1,
                        const CUtensorMap& b2, cudaStream_t st) {
   const AfProblem& p = args.a.p;
-  const int key = (p.mask_kind == AF_MASK_CAUSAL ? 4 : 0) + (p.bias_kind == AF_BIAS_ALIBI ? 2 : 0) + (p.rope ? 1 : 0);
+  const int key = (p.mask_kind == AF_MASK_CAUSAL ? 4 : p.mask_kind == AF_MASK_WINDOW ? 8 : 0) +
+                  (p.bias_kind == AF_BIAS_ALIBI ? 2 : 0) + (p.rope ? 1 : 0);
   switch (key) {
+    case 8: return launch_instance<T, D, MODE, EMASK_WINDOW, false, false>(args, a1, a2, b1, b2, st);
+    case 9: return launch_instance<T, D, MODE, EMASK_WINDOW, false, true>(args, a1, a2, b1, b2, st);
+    case 10: return launch_instance<T, D, MODE, EMASK_WINDOW, true, false>(args, a1, a2, b1, b2, st);
+    case 11: return launch_instance<T, D, MODE, EMASK_WINDOW, true, true>(args, a1, a2, b1, b2, st);
     case 0: return launch_instance<T, D, MODE, EMASK_NONE, false, false>(args, a1, a2, b1, b2, st);
     case 1: return launch_instance<T, D, MODE, EMASK_NONE, false, true>(args, a1, a2, b1, b2, st);
     case 2: return launch_instance<T, D, MODE, EMASK_NONE, true, false>(args, a1, a2, b1, b2, st);

@@ -3,6 +3,7 @@ import pytest
 import torch
 
 import attentionfuse_b200 as af
+from attentionfuse_b200.runtime import _lib
 from attentionfuse_b200.runtime.dispatch import _alibi_slopes
 from oracle import attention_oracle as orc
 from tests._util import assert_close, golden, qkv
@@ -118,3 +119,24 @@ def test_backward_ffma_family_on_half_types(variant, dtype, monkeypatch):
                          ids=lambda s: "x".join(map(str, s)))
 def test_backward_tcgen05_longer(variant, shape):
     check(variant, shape, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window", [1, 64, 200, 513])
+@pytest.mark.parametrize("D", [64, 128])
+def test_window_backward_on_tensor_cores(window, D):
+    """Sliding-window gradients on the tcgen05 kernels: windows narrower than, equal to and wider
+    than the 64-row steps and 128-row stationary tiles, over several tiles, GQA."""
+    B, Hq, Hkv, N, dtype = 1, 4, 2, 700, torch.bfloat16
+    Q, K, V = qkv(1400 + window, B, Hq, Hkv, N, N, D, dtype)
+    dO = orc.randn(1403, (B, Hq, N, D), dtype)
+    p = _lib.AfProblem()
+    from attentionfuse_b200.runtime.dispatch import fill_problem
+    q = Q.to(DEV)
+    fill_problem(p, q, K.to(DEV), V.to(DEV), sm_scale=D ** -0.5, mask_kind=2, window=window)
+    assert _lib.load().af_query_family(p, 1) == _lib.AF_FAMILY_TCGEN05
+    out, dq, dk, dv = grads(make_window(window), Q, K, V, dO)
+    O, dQ, dK, dV = orc.attention_grads(Q, K, V, dO, window=window)
+    assert_close(out, O, dtype, what="window O")
+    assert_close(dq, dQ, dtype, grad=True, what="window dQ")
+    assert_close(dk, dK, dtype, grad=True, what="window dK")
+    assert_close(dv, dV, dtype, grad=True, what="window dV")
