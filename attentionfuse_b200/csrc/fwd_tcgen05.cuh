@@ -50,13 +50,14 @@ enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };  // element-level m
 constexpr int BM = 128;
 constexpr int BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;   // 128 rows x 64 elements x 2 bytes
-// The reference maximum of a row moves only when a tile maximum exceeds it by more than
+// The reference maximum of a softmax stream moves only when a tile maximum exceeds it by more than
 // kRescaleThreshold (log2 units).  A tile processed without looking at its maximum first is accepted
-// when its row sum stays below kRowSumBound: every term is then below the bound too, far inside the
-// f16 range, and a rejected tile has a term above kRowSumBound / 128 = 2^kRescaleThreshold, so the
-// classic pass that follows is certain to move the reference and the next tile is accepted again.
+// when the sum over the thread's 64 columns stays below kRowSumBound: every term is then below the
+// bound too, far inside the f16 range, and a rejected tile has a term above kRowSumBound / 64 = 2^7 >
+// 2^kRescaleThreshold, so the classic pass that follows is certain to move the reference and the
+// next tile is accepted again.
 constexpr float kRescaleThreshold = 6.f;
-constexpr float kRowSumBound = 8192.f;   // 128 * 2^kRescaleThreshold
+constexpr float kRowSumBound = 8192.f;
 
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
