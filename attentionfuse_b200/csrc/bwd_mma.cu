@@ -88,6 +88,15 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
   dq.stat_per_block = blocks ? p.block_m / 128 : 1;
   dq.steps_per_block = blocks ? p.block_n / 64 : 1;
   AF_REQUIRE((int64_t)dq.tiles * p.B * p.H_q <= 0x7fffffff, "too many tiles for one launch");
+  // Persistent launches: one CTA per SM walks its share of the stationary tiles, so that the loads
+  // and first products of the next tile overlap the epilogue of the previous one.
+  int dev = 0, sms = 0;
+  AF_CUDA_OK(cudaGetDevice(&dev));
+  AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  dkv.total_items = dkv.tiles * p.B * p.H_kv;
+  dq.total_items = dq.tiles * p.B * p.H_q;
+  dkv.grid_ctas = (sms > 0 && sms < dkv.total_items) ? sms : dkv.total_items;
+  dq.grid_ctas = (sms > 0 && sms < dq.total_items) ? sms : dq.total_items;
 
   if (p.D == 64) {
     if ((rc = tcb::launch_dkv_d64(p.dtype, dkv, k128, v128, q64, do64, st)) != AF_OK) return rc;

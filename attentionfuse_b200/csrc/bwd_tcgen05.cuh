@@ -56,7 +56,7 @@ template <int D> struct BCfg {
 };
 
 struct BBarriers {
-  uint64_t stat_full;
+  uint64_t stat_full, stat_empty, acc_free;
   uint64_t strm_full[4], strm_empty[4];
   uint64_t xy_full[2], p_full[2], acc_done[2];
   uint32_t tmem_base;
@@ -68,6 +68,8 @@ struct BwdArgs {
   int tiles;            // stationary tiles along the sequence
   int steps_per_block;  // block lists: streamed 64-row steps per listed block
   int stat_per_block;   // block lists: stationary 128-row tiles per block
+  int total_items;      // tiles * B * heads: stationary tiles to process
+  int grid_ctas;        // one persistent CTA per SM (or one per item when there are fewer)
 };
 
 // The streamed steps one stationary tile visits for one head.
@@ -116,6 +118,37 @@ __device__ __forceinline__ StepWalk make_steps(const AfProblem& p, const BwdArgs
   return w;
 }
 
+// One work item = one stationary 128-row tile of one (batch, head).  Items are numbered heaviest
+// first and taken in a zig-zag by the persistent CTAs (item r*G + c in even rounds r, r*G + G-1-c
+// in odd rounds), exactly as in the forward kernel.
+struct BItem {
+  int tile, b, hx, h_kv, t0, total_steps;
+};
+
+template <int MODE, int EMASK>
+__device__ __forceinline__ bool get_bitem(const AfProblem& p, const BwdArgs& args, int round, BItem& bi) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const int64_t w64 = (int64_t)round * G + ((round & 1) ? G - 1 - c : c);
+  if (w64 >= args.total_items) return false;
+  const int w = (int)w64;
+  const int grp = p.H_q / p.H_kv;
+  const int heads = (MODE == MODE_DKV) ? p.H_kv : p.H_q;
+  const int bh_count = p.B * heads;
+  // heaviest tiles first: causal dK/dV work shrinks with the key tile index, dQ work grows with
+  // the query tile index
+  bi.tile = (MODE == MODE_DQ && EMASK == EMASK_CAUSAL) ? (args.tiles - 1 - w / bh_count) : (w / bh_count);
+  const int bh = w % bh_count;
+  bi.b = bh / heads;
+  bi.hx = bh % heads;                                    // kv head (DKV) or query head (DQ)
+  bi.h_kv = (MODE == MODE_DKV) ? bi.hx : bi.hx / grp;
+  bi.t0 = bi.tile * BS;
+  const int heads_per_item = (MODE == MODE_DKV) ? grp : 1;
+  bi.total_steps = 0;                                    // all heads of the group in DKV mode
+  for (int g = 0; g < heads_per_item; ++g)
+    bi.total_steps += make_steps<MODE>(p, args, bi.tile, (MODE == MODE_DKV) ? bi.h_kv * grp + g : bi.hx).cnt;
+  return true;
+}
+
 template <typename T, int D, int MODE, int EMASK, bool ALIBI, bool ROPE>
 __global__ void __launch_bounds__(224, 1)
 bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a1,
@@ -141,20 +174,12 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = p.H_q / p.H_kv;
-  const int heads_here = (MODE == MODE_DKV) ? p.H_kv : p.H_q;
-  const int bh_count = p.B * heads_here;
-  // heaviest tiles first: causal dK/dV work shrinks with the key tile index, dQ work grows with
-  // the query tile index
-  const int tile = (MODE == MODE_DQ && EMASK == EMASK_CAUSAL) ? (args.tiles - 1 - (int)(blockIdx.x / bh_count))
-                                                              : (int)(blockIdx.x / bh_count);
-  const int bh = blockIdx.x % bh_count;
-  const int b = bh / heads_here, hx = bh % heads_here;        // hx: kv head (DKV) or query head (DQ)
-  const int h_kv = (MODE == MODE_DKV) ? hx : hx / group;
-  const int t0 = tile * BS;
   const int n_heads = (MODE == MODE_DKV) ? group : 1;
 
   if (tid == 0) {
     mbar_init(&bars->stat_full, 1);
+    mbar_init(&bars->stat_empty, 1);
+    mbar_init(&bars->acc_free, 128);
     for (int s = 0; s < 4; ++s) {
       mbar_init(&bars->strm_full[s], 1);
       mbar_init(&bars->strm_empty[s], 1);
@@ -176,16 +201,25 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
 
-  // total number of steps of this CTA (all heads of the group in DKV mode)
-  int total_steps = 0;
-  for (int g = 0; g < n_heads; ++g)
-    total_steps += make_steps<MODE>(p, args, tile, (MODE == MODE_DKV) ? h_kv * group + g : hx).cnt;
-
+  // Every role walks the same item sequence.  `it0` counts the steps of the items before the
+  // current one: ring stages, X/Y buffers and barrier phases run on the running count, so that the
+  // loads and the first products of the next item overlap the previous item's epilogue; `qi`
+  // counts the items with at least one step (phases of the stationary-tile and accumulator
+  // hand-overs).
   if (warp == 4) {
     // ============================== producer (TMA + per-step statistics) ==============================
-    if (total_steps > 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_a2); tma_prefetch_desc(&map_b1); tma_prefetch_desc(&map_b2);
+    }
+    BItem bi;
+    int it0 = 0, qi = 0;
+    bool ok = true;
+    for (int round = 0; ok && get_bitem<MODE, EMASK>(p, args, round, bi); ++round) {
+      if (bi.total_steps == 0) continue;
+      const int tile = bi.tile, b = bi.b, hx = bi.hx, h_kv = bi.h_kv, t0 = bi.t0;
+      // the stationary tiles are free once the last S / dP product of the previous item has run
+      if (qi > 0 && !mbar_wait(&bars->stat_empty, (qi - 1) & 1, abort_flag)) break;
       if (lane == 0) {
-        tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_a2); tma_prefetch_desc(&map_b1); tma_prefetch_desc(&map_b2);
         mbar_arrive_expect_tx(&bars->stat_full, 2 * C::STAT_TILE);
         const int ha = (MODE == MODE_DKV) ? h_kv : hx;
 #pragma unroll
@@ -194,8 +228,7 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
           tma_load_4d(smem + C::STAT_TILE + pn * C::STAT_PANEL, &map_a2, &bars->stat_full, pn * 64, t0, ha, b);
         }
       }
-      int it = 0;
-      bool ok = true;
+      int it = it0;                                                   // running step count
       for (int g = 0; g < n_heads && ok; ++g) {
         const int h = (MODE == MODE_DKV) ? h_kv * group + g : hx;
         const int hb = (MODE == MODE_DKV) ? h : h_kv;                 // head of the streamed tensors
@@ -236,25 +269,32 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
           if (lane == 0) mbar_arrive(&bars->strm_full[st]);
         }
       }
+      it0 += bi.total_steps;
+      ++qi;
     }
   } else if (warp == 5) {
     // ============================== MMA issuer 1: S / dP products ==============================
     // Two issuing threads feed the tensor pipe: a tcgen05.mma issue blocks while the pipe's short
     // queue is full, so one thread issuing both kinds leaves the pipe idle during its own barrier
     // waits and commits (measured: 1800 - 2100 cycles per step for 1000 - 1300 cycles of MMA).
-    if (lane == 0 && total_steps > 0) {
+    if (lane == 0) {
       const uint64_t desc_a1 = umma_desc_sw128(sA1, 16, 1024), desc_a2 = umma_desc_sw128(sA2, 16, 1024);
       const uint64_t desc_b1k = umma_desc_sw128(sStage0, 16, 1024);              // streamed tile, K-major
-      bool ok = mbar_wait(&bars->stat_full, 0, abort_flag);
-      for (int it = 0; ok && it < total_steps; ++it) {
+      BItem bi;
+      int it0 = 0, qi = 0;
+      bool ok = true;
+      for (int round = 0; ok && get_bitem<MODE, EMASK>(p, args, round, bi); ++round) {
+      if (bi.total_steps == 0) continue;
+      ok = mbar_wait(&bars->stat_full, qi & 1, abort_flag);
+      for (int it = it0; ok && it < it0 + bi.total_steps; ++it) {     // `it`: running step count
         const int st = it % STAGES, t = it & 1;
-        if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) break;
+        if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
         // X/Y[t] were last used by step it-2.  MODE_DKV: P^T / dS^T overwrite X/Y, so the
         // accumulate MMAs of that step must have run.  MODE_DQ: the element-wise group must have
         // read them (its arrival on p_full).
         if (it >= 2) {
           uint64_t* free_bar = (MODE == MODE_DKV) ? &bars->acc_done[t] : &bars->p_full[t];
-          if (!mbar_wait(free_bar, ((it >> 1) - 1) & 1, abort_flag)) break;
+          if (!mbar_wait(free_bar, ((it >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
         }
         tc_fence_after_sync();
         // Descriptors are built once; k-steps and ring stages only move the start-address field.
@@ -270,15 +310,27 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
                   b2 + (uint64_t)(((kk >> 2) * C::STRM_PANEL + (kk & 3) * 32) >> 4), IDESC_XY, kk > 0 ? 1u : 0u);
         umma_commit(&bars->xy_full[t]);
       }
+      if (ok) umma_commit(&bars->stat_empty);   // the item's last products: the stationary tiles may be refilled
+      it0 += bi.total_steps;
+      ++qi;
+      }
     }
   } else if (warp == 6) {
     // ============================== MMA issuer 2: gradient accumulation ==============================
-    if (lane == 0 && total_steps > 0) {
+    if (lane == 0) {
       const uint64_t desc_b1n = umma_desc_sw128(sStage0, C::STRM_PANEL, 1024);   // streamed tile, N-major
-      for (int it = 0; it < total_steps; ++it) {
+      BItem bi;
+      int it0 = 0, qi = 0;
+      bool ok = true;
+      for (int round = 0; ok && get_bitem<MODE, EMASK>(p, args, round, bi); ++round) {
+      if (bi.total_steps == 0) continue;
+      for (int it = it0; it < it0 + bi.total_steps; ++it) {            // `it`: running step count
         const int st = it % STAGES, t = it & 1;
-        if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) break;
-        if (!mbar_wait(&bars->p_full[t], (it >> 1) & 1, abort_flag)) break;
+        const bool first = it == it0;                                  // overwrites the accumulators
+        if (!mbar_wait(&bars->strm_full[st], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&bars->p_full[t], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+        // the previous item's epilogue must have read the accumulators out
+        if (first && qi > 0 && !mbar_wait(&bars->acc_free, (qi - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint64_t b1 = desc_b1n + (uint64_t)((st * STAGE_BYTES) >> 4), b2 = b1 + (uint64_t)(C::STRM_TILE >> 4);
         const uint32_t xt = tmem + (t ? C::COL_X1 : C::COL_X0), yt = tmem + (t ? C::COL_Y1 : C::COL_Y0);
@@ -287,35 +339,42 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dV += P^T dO
             umma_ts(tmem + C::COL_ACC1, xt + kk * 8, b2 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
-                    (it > 0 || kk > 0) ? 1u : 0u);
+                    (!first || kk > 0) ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dK += dS^T Q
             umma_ts(tmem + C::COL_ACC2, yt + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
-                    (it > 0 || kk > 0) ? 1u : 0u);
+                    (!first || kk > 0) ? 1u : 0u);
         } else {
           const uint32_t dst = tmem + (t ? C::COL_DS1 : C::COL_DS0);
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)      // dQ += dS K
             umma_ts(tmem + C::COL_ACC1, dst + kk * 8, b1 + (uint64_t)((kk * 2048) >> 4), IDESC_ACC,
-                    (it > 0 || kk > 0) ? 1u : 0u);
+                    (!first || kk > 0) ? 1u : 0u);
         }
         umma_commit(&bars->strm_empty[st]);
         umma_commit(&bars->acc_done[t]);
       }
+      it0 += bi.total_steps;
+      ++qi;
+      }
     }
   } else if (warp < 4) {
     // ============================== element-wise group / epilogue ==============================
-    const int srow = t0 + tid;                       // key (DKV) or query row (DQ) of this thread
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const float scale2 = p.sm_scale * kLog2e;
+    BItem bi;
+    int it0 = 0;
+    bool alive = true;
+    for (int round = 0; alive && get_bitem<MODE, EMASK>(p, args, round, bi); ++round) {
+    const int tile = bi.tile, b = bi.b, hx = bi.hx, h_kv = bi.h_kv, t0 = bi.t0, total_steps = bi.total_steps;
+    const int srow = t0 + tid;                       // key (DKV) or query row (DQ) of this thread
     float l2_row = INFINITY, dl_row = 0.f;           // DQ mode: statistics of this thread's query row
     if (MODE == MODE_DQ && srow < p.N_q) {
       const float l = a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)hx * a.lse_stride[1] + (int64_t)srow * a.lse_stride[2]];
       l2_row = (l == -INFINITY) ? INFINITY : l * kLog2e;
       dl_row = a.delta[((int64_t)b * p.H_q + hx) * p.N_q + srow];
     }
-    bool alive = true;
-    int it = 0;
+    int it = it0;                                    // running step count
     for (int g = 0; g < n_heads && alive; ++g) {
       const int h = (MODE == MODE_DKV) ? h_kv * group + g : hx;
       const StepWalk w = make_steps<MODE>(p, args, tile, h);
@@ -402,7 +461,7 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
 
     // ---------------- epilogue ----------------
     if (alive && total_steps > 0) {
-      const int last = total_steps - 1;
+      const int last = it0 + total_steps - 1;
       alive = mbar_wait(&bars->acc_done[last & 1], (last >> 1) & 1, abort_flag);
       tc_fence_after_sync();
     }
@@ -493,6 +552,13 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         }
       }
     }
+    if (alive && total_steps > 0) {
+      // accumulators read out: the next item's first accumulation may overwrite them
+      tc_fence_before_sync();
+      mbar_arrive(&bars->acc_free);
+      it0 += total_steps;
+    }
+    }  // items
   }
 
   tc_fence_before_sync();
@@ -515,10 +581,8 @@ int launch_instance(const BwdArgs& args, const CUtensorMap& a1, const CUtensorMa
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  const AfProblem& p = args.a.p;
-  const int64_t ctas = (int64_t)args.tiles * p.B * (MODE == MODE_DKV ? p.H_kv : p.H_q);
-  if (ctas <= 0) return AF_OK;
-  kern<<<(unsigned)ctas, 224, smem, st>>>(args, a1, a2, b1, b2);
+  if (args.total_items <= 0) return AF_OK;
+  kern<<<(unsigned)args.grid_ctas, 224, smem, st>>>(args, a1, a2, b1, b2);
   count_launch();
   return check_cuda(cudaGetLastError(), "bwd_tcgen05 launch");
 }
