@@ -60,7 +60,7 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
   if (p.rope) {
     void* q_rot = a.workspace;
     void* k_rot = static_cast<char*>(a.workspace) + align256((int64_t)p.B * p.H_q * p.N_q * p.D * 2);
-    if ((rc = tc_launch_prepass(p, q_rot, k_rot, st)) != AF_OK) return rc;
+    if (!a.workspace_holds_rotated && (rc = tc_launch_prepass(p, q_rot, k_rot, st)) != AF_OK) return rc;
     q_ptr = q_rot; k_ptr = k_rot;
     qs[3] = 1; qs[2] = p.D; qs[1] = (int64_t)p.N_q * p.D; qs[0] = qs[1] * p.H_q;
     ks[3] = 1; ks[2] = p.D; ks[1] = (int64_t)p.N_kv * p.D; ks[0] = ks[1] * p.H_kv;

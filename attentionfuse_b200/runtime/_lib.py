@@ -62,6 +62,7 @@ class AfBwdParams(C.Structure):
         ("dk", PTR), ("dk_stride", S4),
         ("dv", PTR), ("dv_stride", S4),
         ("workspace", PTR), ("workspace_bytes", I64),
+        ("workspace_holds_rotated", I32),
     ]
 
 

@@ -23,7 +23,10 @@ class AttnFuseFunction(torch.autograd.Function):
                 "inference path.")
         B, H_q, N_q, _ = Q.shape
         L = torch.empty(B, H_q, N_q, dtype=torch.float32, device=Q.device)
-        out = run_attention(graph, Q, K, V, bias=bias, cos=cos, sin=sin, save_lse=L)
+        kept: list = []
+        out = run_attention(graph, Q, K, V, bias=bias, cos=cos, sin=sin, save_lse=L, keep_workspace=kept)
+        # RoPE: the forward's workspace holds the rotated Q and K; the backward takes it over
+        ctx.rotated = kept[0] if kept else None
         ctx.graph = graph
         ctx.sm_scale = get_or_compile(graph).sm_scale
         ctx.bias, ctx.cos, ctx.sin = bias, cos, sin
@@ -34,7 +37,7 @@ class AttnFuseFunction(torch.autograd.Function):
     def backward(ctx, dO):
         Q, K, V, O, L = ctx.saved_tensors
         dQ, dK, dV = run_backward(ctx.graph, Q, K, V, O, L, dO.contiguous(), ctx.sm_scale,
-                                  bias=ctx.bias, cos=ctx.cos, sin=ctx.sin)
+                                  bias=ctx.bias, cos=ctx.cos, sin=ctx.sin, rotated=ctx.rotated)
         return None, dQ, dK, dV, None, None, None
 
 

@@ -35,7 +35,9 @@ def can_backward(graph: Graph) -> bool:
 
 
 def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_kind=0, slopes=None,
-                    bias=None, cos=None, sin=None, block_lists=None, family=None):
+                    bias=None, cos=None, sin=None, block_lists=None, family=None, rotated=None):
+    """`rotated`: the forward's workspace tensor holding the rotated Q and K (RoPE problems), taken
+    over instead of running the rotation pre-pass again."""
     lib = _lib.load()
     B, H_q, N_q, D = Q.shape
     dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
@@ -56,7 +58,10 @@ def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_ki
     params.dv, params.dv_stride = dV.data_ptr(), _lib.strides(dV)
     need = int(lib.af_bwd_workspace_bytes(C.byref(params)))
     if need > 0:
-        workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
+        if rotated is not None and rotated.numel() >= need and rotated.device == Q.device:
+            workspace, params.workspace_holds_rotated = rotated, 1
+        else:
+            workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
         params.workspace, params.workspace_bytes = workspace.data_ptr(), need
     with torch.cuda.device(Q.device):
         rc = lib.af_bwd(C.byref(params), _lib.current_stream(Q.device))
@@ -67,7 +72,7 @@ def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_ki
 def run_backward(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor,
                  O: torch.Tensor, L: torch.Tensor, dO: torch.Tensor, sm_scale: float,
                  bias: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
-                 sin: Optional[torch.Tensor] = None, alibi_slopes=None):
+                 sin: Optional[torch.Tensor] = None, alibi_slopes=None, rotated=None):
     """Return (dQ, dK, dV).  `sm_scale` is the scale the forward used."""
     bundle = get_or_compile(graph)
     slopes = None
@@ -82,4 +87,4 @@ def run_backward(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor
         c, s = _rope_table(cos, "cos", Q), _rope_table(sin, "sin", Q)
     return launch_backward(Q, K, V, O, L, dO, sm_scale=sm_scale, mask_kind=bundle.mask_kind,
                            window=bundle.window, bias_kind=bundle.bias_kind, slopes=slopes,
-                           bias=bias if bundle.has_additive_bias else None, cos=c, sin=s)
+                           bias=bias if bundle.has_additive_bias else None, cos=c, sin=s, rotated=rotated)

@@ -98,8 +98,10 @@ def validate_qkv(Q, K, V):
 
 def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, norm_kind=0,
                    slopes=None, bias=None, cos=None, sin=None, save_lse=None,
-                   block_lists=None, family=None, q_offset=0):
-    """Fill AfFwdParams and call af_fwd on the current stream."""
+                   block_lists=None, family=None, q_offset=0, keep_workspace=None):
+    """Fill AfFwdParams and call af_fwd on the current stream.  `keep_workspace`, a list, receives
+    the workspace tensor when the call used one (the rotated Q and K of a RoPE problem, which the
+    backward can take over instead of rotating again)."""
     lib = _lib.load()
     params = _lib.AfFwdParams()
     keep: list = []
@@ -115,6 +117,8 @@ def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, 
     if need > 0 and os.environ.get("ATTNFUSE_ROPE_IN_KERNEL", "0") != "1":
         workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
         params.workspace, params.workspace_bytes = workspace.data_ptr(), need
+        if keep_workspace is not None:
+            keep_workspace.append(workspace)
     with torch.cuda.device(Q.device):
         rc = lib.af_fwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_fwd")
@@ -126,7 +130,7 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
                   sin: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                   save_lse: Optional[torch.Tensor] = None, *, alibi_slopes=None,
                   kv_lens: Optional[torch.Tensor] = None, family: Optional[int] = None,
-                  q_offset: Optional[int] = None) -> torch.Tensor:
+                  q_offset: Optional[int] = None, keep_workspace: Optional[list] = None) -> torch.Tensor:
     """Run the fused forward; returns O with Q's shape and dtype.
 
     Extensions over the reference signature (all keyword-only): ``alibi_slopes`` overrides the
@@ -191,4 +195,5 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
     return launch_forward(Q, K, V, out, sm_scale=bundle.sm_scale, mask_kind=bundle.mask_kind,
                           window=bundle.window, bias_kind=bundle.bias_kind,
                           norm_kind=bundle.norm_kind, slopes=slopes, bias=bias, cos=c, sin=s,
-                          save_lse=save_lse, family=family, q_offset=q_offset or 0)
+                          save_lse=save_lse, family=family, q_offset=q_offset or 0,
+                          keep_workspace=keep_workspace)

@@ -107,6 +107,9 @@ typedef struct AfBwdParams {
   void* dv; int64_t dv_stride[4];
   void*   workspace;                  /* optional scratch, see af_bwd_workspace_bytes      */
   int64_t workspace_bytes;
+  int32_t workspace_holds_rotated;    /* 1: the workspace already holds the rotated Q and K of
+                                         this problem, as af_fwd left them in its own workspace
+                                         (same layout); the RoPE pre-pass is then skipped      */
 } AfBwdParams;
 
 /* Split-K decode (query length 1).  Workspaces are fp32:
