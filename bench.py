@@ -319,17 +319,47 @@ def main():
     kernel_tflops = flops / (kernel_ms * 1e-3) / 1e12
     del Qr, Kr
 
-    # ---- end to end: pinned host buffers in, O back to the host, through the DSL call
-    Qd, Kd, Vd = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+    # ---- end to end: pinned host buffers in, O back to the host, through the public call.  The
+    #      step is the call pattern of a host that owns the tensors: one chunk at a time, the next
+    #      chunk's host-to-device copy and the previous chunk's device-to-host copy (separate
+    #      streams, PCIe is full duplex) overlapping the chunk in flight.  Every byte of Q, K, V goes
+    #      up and every byte of O comes down inside the timed region of every step.
+    Qd, Kd, Vd, Od = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V), torch.empty_like(Q)
     Oh = torch.empty(Q.shape, dtype=Q.dtype).pin_memory()
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    # chunks: (batch row, range of kv heads with their query heads) -- contiguous blocks of the
+    # (B, H, N, D) tensors, the unit the multi-GPU partition deals out.  One chunk per batch row
+    # measured best (4.8 ms; four chunks per row 5.1 ms, one chunk for everything 6.6 ms).
+    grp, kv_per_chunk = CFG4["H_q"] // CFG4["H_kv"], CFG4["H_kv"]
+    chunks = [(b, h0, h0 + kv_per_chunk) for b in range(Q.shape[0]) for h0 in range(0, CFG4["H_kv"], kv_per_chunk)]
+    ev_in = [torch.cuda.Event() for _ in chunks]
+    ev_out = [torch.cuda.Event() for _ in chunks]
 
     def e2e_step():
-        Qd.copy_(Qp, non_blocking=True); Kd.copy_(Kp, non_blocking=True); Vd.copy_(Vp, non_blocking=True)
-        o = causal_rope(Qd, Kd, Vd, cos=cos, sin=sin)
-        Oh.copy_(o, non_blocking=True)
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur)                      # the device buffers of the previous step are consumed
+        with torch.cuda.stream(s_in):
+            for i, (b, h0, h1) in enumerate(chunks):
+                Qd[b, h0 * grp:h1 * grp].copy_(Qp[b, h0 * grp:h1 * grp], non_blocking=True)
+                Kd[b, h0:h1].copy_(Kp[b, h0:h1], non_blocking=True)
+                Vd[b, h0:h1].copy_(Vp[b, h0:h1], non_blocking=True)
+                ev_in[i].record(s_in)
+        for i, (b, h0, h1) in enumerate(chunks):
+            cur.wait_event(ev_in[i])
+            run_attention(graph, Qd[b:b + 1, h0 * grp:h1 * grp], Kd[b:b + 1, h0:h1], Vd[b:b + 1, h0:h1],
+                          cos=cos, sin=sin, out=Od[b:b + 1, h0 * grp:h1 * grp])
+            ev_out[i].record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_out[i])
+                Oh[b, h0 * grp:h1 * grp].copy_(Od[b, h0 * grp:h1 * grp], non_blocking=True)
+        cur.wait_stream(s_out)                     # the step ends when the last chunk of O is on the host
 
     for _ in range(2):
         e2e_step()
+    step()                                         # the device-resident step on the same inputs
+    torch.cuda.synchronize()
+    if (Oh.to(dev).float() - out.float()).abs().max().item() > 1e-3:
+        raise RuntimeError("end-to-end step does not reproduce the device-resident result")
     e2e_steps = max(3, min(args.steps, 10))
     e2e_ms = time_region(e2e_step, e2e_steps, dist_on) / e2e_steps
     h2d = Qp.numel() * 2 + Kp.numel() * 2 + Vp.numel() * 2
