@@ -170,3 +170,23 @@ def test_cfg5_bigbird_per_head():
     # control: an all-active mask equals dense attention
     full = af.BlockMask.from_dense(torch.ones(nb, nb, dtype=torch.bool), blk, blk, device=DEV)
     assert orc.rel_fro(bs_attn(Q, K, V, block_mask=full).float().cpu(), dense(Q, K, V).float().cpu()) < 2e-3
+
+
+@pytest.mark.parametrize("variant", ["causal_rope", "window"])
+def test_long_sequence_chunks_agree_with_the_whole(variant):
+    """A 16k-token problem: the last query chunk run on its own against the full key axis
+    (`q_offset`) equals the same rows of the whole problem, the oracle checks those rows, and
+    every row of P sums to one (V = 1 gives O = 1)."""
+    B, Hq, Hkv, N, D, dtype = 1, 8, 2, 16384, 128, torch.bfloat16
+    Q, K, V = gpu_randn(9100, (B, Hq, N, D), dtype), gpu_randn(9101, (B, Hkv, N, D), dtype), gpu_randn(9102, (B, Hkv, N, D), dtype)
+    cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
+    fn, kw, okw = (causal_rope, dict(cos=cos.to(DEV), sin=sin.to(DEV)), dict(causal=True, cos=cos, sin=sin)) \
+        if variant == "causal_rope" else (window256, {}, dict(window=256))
+    whole = fn(Q, K, V, **kw)
+    n_q, off = 384, N - 384
+    chunk = fn(Q[:, :, off:].contiguous(), K, V, q_offset=off, **kw)
+    assert (chunk.float() - whole[:, :, off:].float()).abs().max().item() <= 4e-3
+    want = orc.attention(Q[:, :, off:].cpu(), K.cpu(), V.cpu(), q_offset=off, **okw)
+    assert_close(chunk, want, dtype, what=f"16k {variant} chunk")
+    ones = fn(Q, K, torch.ones_like(V), **kw)
+    assert (ones.float() - 1).abs().max().item() < 1e-2
