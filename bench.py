@@ -273,8 +273,6 @@ def main():
     dev = torch.device("cuda", local_rank)
     dist_on = world > 1
     if dist_on:
-        # stdout carries the one JSON line: NCCL's own messages (its version banner) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
     pk, pk_kind = peaks()
