@@ -175,6 +175,26 @@ def strides(t, n: int = 4):
     return (I64 * n)(*[int(s) for s in t.stride()])
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def on_device(device):
+    """Context that makes `device` current for a launch; free when it already is (the usual
+    case), a torch.cuda.device switch otherwise."""
+    import torch
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def current_stream(device) -> int:
     import torch
     return torch.cuda.current_stream(device).cuda_stream

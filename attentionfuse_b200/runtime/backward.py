@@ -63,7 +63,7 @@ def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_ki
         else:
             workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
         params.workspace, params.workspace_bytes = workspace.data_ptr(), need
-    with torch.cuda.device(Q.device):
+    with _lib.on_device(Q.device):
         rc = lib.af_bwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_bwd")
     return dQ, dK, dV

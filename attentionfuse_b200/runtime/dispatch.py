@@ -119,7 +119,7 @@ def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, 
         params.workspace, params.workspace_bytes = workspace.data_ptr(), need
         if keep_workspace is not None:
             keep_workspace.append(workspace)
-    with torch.cuda.device(Q.device):
+    with _lib.on_device(Q.device):
         rc = lib.af_fwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_fwd")
     return out

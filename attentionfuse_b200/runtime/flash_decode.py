@@ -104,7 +104,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         p.o, p.o_stride = out.data_ptr(), _lib.strides(out)
     if partial is not None:
         p.partial = partial.data_ptr()
-    with torch.cuda.device(Q.device):
+    with _lib.on_device(Q.device):
         stream = _lib.current_stream(Q.device)
         _lib.check(lib.af_decode_split(C.byref(p), stream), "af_decode_split")
         if exchange is not None:
@@ -122,7 +122,7 @@ def combine_gathered(gathered: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     G, B, H_q, D1 = gathered.shape
     assert gathered.dtype == torch.float32 and gathered.is_contiguous()
     lib = _lib.load()
-    with torch.cuda.device(out.device):
+    with _lib.on_device(out.device):
         rc = lib.af_decode_combine_gathered(gathered.data_ptr(), G, B, H_q, D1 - 1,
                                             _lib.dtype_code(out.dtype), out.data_ptr(),
                                             _lib.strides(out), _lib.current_stream(out.device))
