@@ -77,3 +77,21 @@ def test_offsets_are_validated_and_cross_attention_rule_stays():
     cos, sin = orc.build_rope_cache(256, D, 10000.0, torch.bfloat16)
     with pytest.raises(ValueError, match="cos/sin"):
         rope(Q.to(DEV), K.to(DEV), V.to(DEV), cos=cos.to(DEV), sin=sin.to(DEV), q_offset=250)
+
+
+@pytest.mark.parametrize("variant", ["causal_rope", "causal_rope_alibi", "window"])
+def test_single_query_step_with_masks_and_rotation(variant):
+    """A decode step (one query row at the end of the cache) through graphs the split-K decode
+    path does not take -- rotation, ALiBi with a causal mask, sliding window: the forward kernels
+    serve it with the row placed at position N_kv - 1."""
+    dtype, B, Hq, Hkv, N_kv, D, window = torch.bfloat16, 2, 8, 2, 1500, 128, 150
+    Qfull, K, V = qkv(3500, B, Hq, Hkv, N_kv, N_kv, D, dtype)
+    off = N_kv - 1
+    Q1 = Qfull[:, :, off:].contiguous()
+    cos, sin = orc.build_rope_cache(N_kv, D, 10000.0, dtype)
+    fn = graphs(Hq, window)[variant]
+    kw = dict(cos=cos.to(DEV), sin=sin.to(DEV)) if "rope" in variant else {}
+    got = fn(Q1.to(DEV), K.to(DEV), V.to(DEV), q_offset=off, **kw)
+    want = orc.attention(Q1, K, V, q_offset=off, **oracle_kwargs(variant, Hq, dtype, window, cos, sin))
+    assert got.shape == (B, Hq, 1, D)
+    assert_close(got, want, dtype, what=f"single-row step {variant}")
