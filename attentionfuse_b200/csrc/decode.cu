@@ -429,6 +429,10 @@ int validate_decode(const AfDecodeParams& a) {
   AF_REQUIRE(a.num_splits >= 1, "num_splits must be >= 1");
   AF_REQUIRE((int64_t)a.B * a.H_kv * ((a.H_q / a.H_kv + 63) / 64) <= 65535, "B*H_kv too large for one launch");
   AF_REQUIRE(a.ws_m && a.ws_l && a.ws_acc, "decode workspaces must be non-NULL");
+  // the combine reads ws_acc rows as float4 (D = 128) / float2 (D = 64); the tensor-core split
+  // epilogue stores float4
+  AF_REQUIRE(((uintptr_t)a.ws_acc & 15) == 0, "ws_acc must be 16-byte aligned");
+  AF_REQUIRE(((uintptr_t)a.ws_m & 3) == 0 && ((uintptr_t)a.ws_l & 3) == 0, "ws_m / ws_l must be 4-byte aligned");
   return AF_OK;
 }
 
@@ -474,22 +478,26 @@ int launch_decode_static(const AfDecodeParams& in, cudaStream_t st) {
     a.num_splits = af_decode_num_splits(a.B, a.H_q, a.H_kv, a.N_kv, sms);
   }
   AF_REQUIRE(a.B > 0 && a.H_q > 0 && a.D > 0, "bad sizes");
+  AF_REQUIRE(a.o || a.partial, "combine needs o or partial");
   const size_t rows = (size_t)a.num_splits * a.B * a.H_q;
-  const size_t need = rows * ((size_t)a.D + 2);
+  // m and l each take rows rounded up to 4 floats, so that acc starts on a 16-byte boundary
+  const size_t rows_pad = (rows + 3) & ~(size_t)3;
+  const size_t need = 2 * rows_pad + rows * (size_t)a.D;
   if (need > kStaticScratchFloats)
     return fail(AF_ERR_WORKSPACE,
-                "af_decode_static: num_splits*B*H_q*(D+2) = %zu floats exceeds the built-in scratch of %zu floats "
+                "af_decode_static: the partials of num_splits*B*H_q rows need %zu floats, which exceeds the built-in scratch of %zu floats "
                 "(%d bytes); use af_decode_split/af_decode_combine with caller workspaces",
                 need, (size_t)kStaticScratchFloats, (int)AF_DECODE_STATIC_SCRATCH_BYTES);
   float* base = nullptr;
   int rc = static_scratch_address(&base);
   if (rc != AF_OK) return rc;
-  // Layout: m[rows], l[rows], acc[rows][D].  The split kernel writes every row of all three
+  // Layout: m[rows_pad], l[rows_pad], acc[rows][D].  The split kernel writes every row of all three
   // (empty splits write m = -inf, l = 0, acc = 0), so nothing left by an earlier call is read
   // and nothing needs clearing.
   a.ws_m = base;
-  a.ws_l = base + rows;
-  a.ws_acc = base + 2 * rows;
+  a.ws_l = base + rows_pad;
+  a.ws_acc = base + 2 * rows_pad;
+  if ((rc = validate_decode(a)) != AF_OK) return rc;   // nothing is launched on a bad parameter block
   if ((rc = launch_decode_split(a, st)) != AF_OK) return rc;
   return launch_decode_combine(a, st);
 }

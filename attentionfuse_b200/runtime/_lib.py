@@ -128,7 +128,7 @@ def load() -> C.CDLL:
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
         lib.af_decode_num_splits.argtypes = [I32, I32, I32, I32, I32]
         lib.af_query_family.argtypes = [C.POINTER(AfProblem), I32]
-        for name in ("af_fwd", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine",
+        for name in ("af_fwd", "af_bwd", "af_decode_split", "af_decode_combine",
                      "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
                      "af_abi_version"):
             getattr(lib, name).restype = I32

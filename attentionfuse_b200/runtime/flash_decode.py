@@ -52,9 +52,13 @@ def _pick_num_splits(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int =
 
 
 def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device):
-    ws = torch.empty(num_splits * B * H_q * (D + 2), dtype=torch.float32, device=device)
+    """(m, l, acc) partials carved from one allocation.  m and l each take the row count rounded
+    up to 4 floats so that acc, which the kernels access with 16-byte vectors, starts on a
+    16-byte boundary for every row count."""
     n = num_splits * B * H_q
-    return ws[:n], ws[n:2 * n], ws[2 * n:]
+    n_pad = (n + 3) & ~3
+    ws = torch.empty(2 * n_pad + n * D, dtype=torch.float32, device=device)
+    return ws[:n], ws[n_pad:n_pad + n], ws[2 * n_pad:]
 
 
 def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor,

@@ -113,7 +113,9 @@ typedef struct AfBwdParams {
 } AfBwdParams;
 
 /* Split-K decode (query length 1).  Workspaces are fp32:
- *   ws_m, ws_l : [num_splits, B, H_q]      ws_acc : [num_splits, B, H_q, D]            */
+ *   ws_m, ws_l : [num_splits, B, H_q]      ws_acc : [num_splits, B, H_q, D]
+ * ws_acc must be 16-byte aligned (the kernels access its rows with 16-byte vectors); when the
+ * three arrays are carved from one allocation, round the m and l parts up to 4 floats each.  */
 typedef struct AfDecodeParams {
   int32_t dtype;
   int32_t B, H_q, H_kv, N_kv, D;
@@ -174,8 +176,9 @@ AF_API int af_decode_combine(const AfDecodeParams* params, af_stream_t stream);
  * cudaMalloc / cudaFree and calls no allocating library routine.
  *
  * params: as for af_decode_split + af_decode_combine; ws_m / ws_l / ws_acc are ignored, and
- * num_splits <= 0 lets the library pick.  The problem must satisfy
- *     num_splits * B * H_q * (D + 2) * 4 bytes <= AF_DECODE_STATIC_SCRATCH_BYTES,
+ * num_splits <= 0 lets the library pick.  With rows = num_splits * B * H_q the problem must
+ * satisfy
+ *     (2 * roundup(rows, 4) + rows * D) * 4 bytes <= AF_DECODE_STATIC_SCRATCH_BYTES,
  * otherwise AF_ERR_WORKSPACE is returned and nothing is launched.
  *
  * The first call on each device looks up the array's device address (the device must be

@@ -65,6 +65,33 @@ def test_host_only_entry_points():
     assert lib.af_decode_static(None, None) == -1
 
 
+def test_misaligned_decode_workspace_is_refused_before_any_launch():
+    """The combine reads ws_acc with 16-byte vectors: a ws_acc that is not 16-byte aligned is an
+    invalid-argument error on the host (checked before the first CUDA call, so it runs here)."""
+    lib = _lib.load()
+    p = _lib.AfDecodeParams()
+    p.dtype, p.B, p.H_q, p.H_kv, p.N_kv, p.D = _lib.AF_BF16, 1, 3, 1, 1536, 128
+    p.sm_scale, p.num_splits = 0.088, 3
+    base = 0x10000
+    p.ws_m, p.ws_l, p.ws_acc = base, base + 4 * 9, base + 8 * 9      # the unpadded layout: 8-byte aligned
+    assert lib.af_decode_split(C.byref(p), None) == -1
+    assert "ws_acc" in _lib.last_error()
+    assert lib.af_decode_combine(C.byref(p), None) == -1
+    for rows in (1, 3, 9, 15, 16, 45):
+        n_pad = (rows + 3) & ~3
+        assert (2 * n_pad * 4) % 16 == 0
+
+
+def test_int64_entry_points_return_int64():
+    """Every export the header declares as int64_t is bound with a 64-bit restype."""
+    lib = _lib.load()
+    text = HEADER.read_text()
+    wide = sorted(set(re.findall(r"AF_API\s+int64_t\s+(af_\w+)\s*\(", text)))
+    assert "af_bwd_workspace_bytes" in wide and "af_fwd_workspace_bytes" in wide
+    for name in wide:
+        assert getattr(lib, name).restype is C.c_int64, name
+
+
 def test_missing_library_is_loud(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")

@@ -73,6 +73,24 @@ def test_decode_golden_and_fp32_route():
     assert_close(got, orc.attention(Q, K, V, kv_lens=g["kv_lens"]), torch.bfloat16, what="golden ragged bf16")
 
 
+@pytest.mark.parametrize("heads", [(3, 1), (5, 5), (9, 3), (1, 1)], ids=lambda h: f"{h[0]}q{h[1]}kv")
+@pytest.mark.parametrize("splits", [1, 3, 5])
+@pytest.mark.parametrize("B", [1, 3])
+def test_odd_partial_row_counts(heads, splits, B):
+    """num_splits * B * H_q odd: the (m, l, acc) partials are carved from one allocation, and acc
+    must start on a 16-byte boundary whatever the row count."""
+    Hq, Hkv = heads
+    L, D = 1536, 128
+    Q, K, V = qkv(990 + Hq, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+    lens = lens_for(17 + B, B, L)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    out = torch.full_like(q, float("nan"))
+    run_flash_decode(None, q, k, v, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens.to(DEV), num_splits=splits)
+    assert_close(out, orc.attention(Q, K, V, kv_lens=lens), torch.bfloat16, what=f"odd rows {heads} S={splits} B={B}")
+    if splits == 3:   # the split count the heuristic picks at this length goes the same way
+        assert_close(dense(q, k, v), orc.attention(Q, K, V), torch.bfloat16, what=f"odd rows auto {heads} B={B}")
+
+
 @pytest.mark.parametrize("splits", [1, 2, 7, 16])
 def test_split_counts_agree(splits):
     B, Hq, Hkv, L, D = 2, 32, 8, 2048, 128

@@ -44,6 +44,8 @@ def test_static_scratch_decode_matches_regular_path_twice():
     cases = [  # B, H_q, H_kv, L, D, dtype
         (4, 32, 8, 4096, 128, torch.bfloat16),
         (2, 16, 2, 1500, 64, torch.float16),
+        (3, 9, 3, 1536, 128, torch.bfloat16),      # an odd number of partial rows
+        (1, 5, 5, 1536, 128, torch.float16),
     ]
     for i, (B, Hq, Hkv, L, D, dt) in enumerate(cases):
         Q, K, V = qkv(7000 + 10 * i, B, Hq, Hkv, 1, L, D, dt)
@@ -66,7 +68,7 @@ def test_static_scratch_rejects_oversized_problem():
     Q, K, V = (torch.zeros(B, h, n, D, dtype=torch.bfloat16, device=DEV) for h, n in ((Hq, 1), (Hkv, L), (Hkv, L)))
     out = torch.zeros_like(Q)
     splits = 4
-    assert splits * B * Hq * (D + 2) * 4 > SCRATCH_BYTES
+    assert splits * B * Hq * (D + 2) * 4 > SCRATCH_BYTES      # rows are a multiple of 4 here: no padding
     rc = decode_static(Q, K, V, out, num_splits=splits)
     assert rc == -4                                   # AF_ERR_WORKSPACE, nothing launched
     assert "exceeds the built-in scratch" in _lib.last_error()
