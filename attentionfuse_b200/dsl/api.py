@@ -104,9 +104,8 @@ def attention(fn: Callable) -> Callable:
         if MaskKind.BLOCK_SPARSE in mask_kinds:
             if block_mask is None:
                 raise RuntimeError(
-                    "Graph uses af.block_sparse(); pass a BlockMask via "
-                    "block_mask=<BlockMask> at call time. Build one via "
-                    "create_block_mask(predicate, Q_LEN, KV_LEN).")
+                    "a block-sparse graph needs its block lists at call time: "
+                    "fn(Q, K, V, block_mask=create_block_mask(predicate, Q_LEN, KV_LEN))")
             from ..runtime.block_mask import BlockMask, run_block_sparse
             if not isinstance(block_mask, BlockMask):
                 raise TypeError("block_mask must be an attnfuse.BlockMask")

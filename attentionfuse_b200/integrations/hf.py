@@ -69,6 +69,17 @@ def _is_chunk_causal_mask(mask: Optional[torch.Tensor], N_q: int, N_kv: int) -> 
     return bool((seen == want).all().item())
 
 
+def _every_key_visible_to_last_row(mask: Optional[torch.Tensor]) -> bool:
+    """In a causal triangle (square, or a chunk at the end of a cache, or a single query row) the
+    last query row sees every key.  A padded batch masks whole key columns for some rows of the
+    batch, which shows up here; such masks must not be replaced by the plain causal rule."""
+    if mask is None:
+        return True
+    last = mask[..., -1, :]
+    seen = last if mask.dtype == torch.bool else last > torch.finfo(mask.dtype).min / 2
+    return bool(seen.all().item())
+
+
 def attnfuse_attention_forward(module: torch.nn.Module, query: torch.Tensor, key: torch.Tensor,
                                value: torch.Tensor, attention_mask: Optional[torch.Tensor],
                                dropout: float = 0.0, scaling: Optional[float] = None,
@@ -82,14 +93,22 @@ def attnfuse_attention_forward(module: torch.nn.Module, query: torch.Tensor, key
     needs_fallback = not chunk and (dropout > 0.0 or not _is_pure_causal_mask(attention_mask, N_q, N_kv))
     if not chunk and attention_mask is not None and N_q != N_kv and N_q > 1:
         needs_fallback = True
+    if is_causal is None:
+        is_causal = getattr(module, "is_causal", True)
+    # causal without a mask over a rectangular score matrix: the reference raises here
+    # (attnfuse/runtime/dispatch.py:140-148); leave the alignment rule to SDPA rather than
+    # silently computing dense attention
+    if attention_mask is None and bool(is_causal) and 1 < N_q != N_kv:
+        needs_fallback = True
+    # the corner probes above accept a padded batch's mask; a fully masked key column gives it away
+    if not needs_fallback and not _every_key_visible_to_last_row(attention_mask):
+        needs_fallback = True
     if needs_fallback:
         from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
         return ALL_ATTENTION_FUNCTIONS["sdpa"](
             module, query, key, value, attention_mask,
             dropout=dropout, scaling=scaling, is_causal=is_causal, **kwargs)
 
-    if is_causal is None:
-        is_causal = getattr(module, "is_causal", True)
     causal_for_us = chunk or (bool(is_causal) and N_q > 1 and N_q == N_kv)
     attn_fn = _get_attn_fn(query.shape[-1], query.dtype, causal_for_us, scaling)
     B, H, _, D = query.shape

@@ -93,6 +93,33 @@ def test_backward_golden():
     assert_close(dv, g["dV_rope"], torch.float32, grad=True, what="dV rope")
 
 
+@pytest.mark.parametrize("shape", [(1, 4, 4, 64, 64), (2, 8, 2, 130, 64), (1, 4, 1, 200, 128), (1, 2, 2, 50, 32)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_causal", [False, True], ids=["bias", "causal_bias"])
+def test_additive_bias_backward(shape, dtype, with_causal):
+    """Gradients of a graph with an additive (B, H, N, N) bias (the reference's can_backward
+    excludes it, attnfuse/runtime/backward.py:69-80; here it runs on the exact kernels).  The
+    bias itself receives no gradient, as in the reference's autograd contract."""
+    B, Hq, Hkv, N, D = shape
+
+    @af.attention
+    def fn(Q, K, V):
+        s = af.additive_bias(af.scaled_dot_product(Q, K))
+        return af.softmax(af.causal(s) if with_causal else s) @ V
+
+    Q, K, V = qkv(1300, B, Hq, Hkv, N, N, D, dtype)
+    dO = orc.randn(1303, (B, Hq, N, D), dtype)
+    bias = orc.randn(1304, (B, Hq, N, N), dtype)
+    out, dq, dk, dv = grads(fn, Q, K, V, dO, bias=bias.to(DEV))
+    assert out.requires_grad
+    O, dQ, dK, dV = orc.attention_grads(Q, K, V, dO, causal=with_causal, bias=bias.float())
+    assert_close(out, O, dtype, what="bias O")
+    assert_close(dq, dQ, dtype, grad=True, what="bias dQ")
+    assert_close(dk, dK, dtype, grad=True, what="bias dK")
+    assert_close(dv, dV, dtype, grad=True, what="bias dV")
+
+
 def test_no_grad_path_and_unsupported_falls_through():
     Q, K, V = qkv(1200, 1, 2, 2, 64, 64, 64, torch.float16)
 

@@ -109,6 +109,18 @@ def test_cfg4_forward_backward():
     assert torch.isfinite(q.grad).all() and torch.isfinite(k.grad).all() and torch.isfinite(v.grad).all()
 
 
+def test_cfg4_forward_whole_tensor():
+    """Llama-3-8B layer shape forward, causal + RoPE(5e5), bf16: every one of the 32 (batch, kv
+    head) groups against the oracle (chunked, so the score matrix stays at one group)."""
+    B, Hq, Hkv, N, D = 4, 32, 8, 4096, 128
+    dt = torch.bfloat16
+    Q, K, V = (gpu_randn(4100 + i, (B, h, N, D), dt) for i, h in enumerate((Hq, Hkv, Hkv)))
+    cos, sin = orc.build_rope_cache(N, D, 500000.0, dt)
+    out = causal_rope(Q, K, V, cos=cos.to(DEV), sin=sin.to(DEV))
+    want = orc.attention_chunked(Q.cpu(), K.cpu(), V.cpu(), causal=True, cos=cos, sin=sin)
+    assert_close(out, want, dt, what="cfg4 forward, all 32 groups")
+
+
 @pytest.mark.parametrize("heads", [(32, 8), (64, 8), (64, 1)], ids=lambda h: f"{h[0]}q{h[1]}kv")
 @pytest.mark.parametrize("L", [16384, 32768])
 def test_cfg3_decode(heads, L):

@@ -152,3 +152,34 @@ def test_sharded_decode_world2_gloo(fail_rank):
         assert all(v < 1e-5 for v in ret.values()), dict(ret)
     else:
         assert all("NaN log-sum-exp" in v and "[1]" in v for v in ret.values()), dict(ret)
+
+
+def test_hf_hook_hands_padded_batches_and_unaligned_causal_to_sdpa(monkeypatch):
+    """Masks the kernel's plain causal rule cannot express go to the SDPA backend untouched: a
+    left-padded batch (whole key columns masked for one row of the batch) and causal attention
+    over a rectangular score matrix without a mask.  The fall-back is decided on the host, so no
+    GPU is involved."""
+    pytest.importorskip("transformers")
+    import attentionfuse_b200.integrations.hf as hf
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+    calls = []
+
+    def fake_sdpa(module, q, k, v, mask, **kw):
+        calls.append(kw.get("is_causal"))
+        return torch.zeros(q.shape[0], q.shape[2], q.shape[1], q.shape[3]), None
+    monkeypatch.setitem(ALL_ATTENTION_FUNCTIONS, "sdpa", fake_sdpa)
+    B, H, N, D = 2, 2, 8, 16
+    q = k = v = torch.zeros(B, H, N, D)
+    neg = torch.finfo(torch.float32).min
+    mask = torch.triu(torch.full((N, N), neg), diagonal=1).expand(B, 1, N, N).clone()
+    assert hf._every_key_visible_to_last_row(mask) and hf._is_pure_causal_mask(mask, N, N)
+    mask[1, :, :, :3] = neg                               # row 1 of the batch is left-padded by 3
+    assert hf._is_pure_causal_mask(mask, N, N)            # the corner probe alone is fooled
+    hf.attnfuse_attention_forward(torch.nn.Identity(), q, k, v, mask)
+    assert len(calls) == 1
+    step_mask = torch.zeros(B, 1, 1, N)
+    step_mask[1, :, :, :3] = neg                          # the same padding during a decode step
+    hf.attnfuse_attention_forward(torch.nn.Identity(), q[:, :, :1], k, v, step_mask)
+    assert len(calls) == 2
+    hf.attnfuse_attention_forward(torch.nn.Identity(), q[:, :, :4], k, v, None, is_causal=True)
+    assert len(calls) == 3 and calls[2] is True
