@@ -108,6 +108,11 @@ int64_t af_bwd_workspace_bytes(const AfBwdParams* params) {
   return bwd_mma_workspace_bytes(*params);
 }
 
+int64_t af_bwd_dq_accum_bytes(const AfBwdParams* params) {
+  if (params == nullptr || params->p.family == AF_FAMILY_FFMA) return 0;
+  return bwd_mma_dq_accum_bytes(*params);
+}
+
 int af_decode_split(const AfDecodeParams* params, af_stream_t stream) {
   if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
   return launch_decode_split(*params, static_cast<cudaStream_t>(stream));

@@ -1,12 +1,84 @@
 // Host side of the tcgen05 backward: support predicate, workspace, TMA descriptors, and the
-// three launches (delta, dK/dV, dQ).
+// launches: delta, then either the two passes (dK/dV, dQ) or -- head_dim 128 with a dQ
+// accumulator from the caller -- the single fused pass followed by the dQ finishing kernel.
+#include <cstdlib>
+
 #include "bwd_tcgen05.cuh"
 
 namespace af {
 
 namespace {
 int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
+
+// dQ accumulator of the fused pass: fp32 (B, H_q, N_q, D), then 256 bytes holding the item counter.
+int64_t dq_accum_floats(const AfProblem& p) { return (int64_t)p.B * p.H_q * p.N_q * p.D; }
+
+// dq = T(scale * R^T(acc)): the fused pass leaves scale-free, still-rotated sums in `acc`.  One
+// thread per pair of 8-element chunks (d, d + D/2) of one row.
+template <typename T, int D, bool ROPE>
+__global__ void bwd_dq_finish_kernel(const float* __restrict__ acc, const AfBwdParams a, int64_t rows) {
+  constexpr int HC = D / 16;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = idx / HC;
+  const int c = (int)(idx - row * HC);
+  if (row >= rows) return;
+  const AfProblem& p = a.p;
+  const int n = (int)(row % p.N_q);
+  const int64_t bh = row / p.N_q;
+  const int h = (int)(bh % p.H_q), b = (int)(bh / p.H_q);
+  const float4* src_lo = reinterpret_cast<const float4*>(acc + row * D + c * 8);
+  const float4* src_hi = reinterpret_cast<const float4*>(acc + row * D + D / 2 + c * 8);
+  const float4 l0 = src_lo[0], l1 = src_lo[1], h0 = src_hi[0], h1 = src_hi[1];
+  float gl[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+  float gh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { gl[i] *= p.sm_scale; gh[i] *= p.sm_scale; }
+  if (ROPE) {
+    const T* cos_row = reinterpret_cast<const T*>(p.cos) + (int64_t)n * p.rope_stride_n;
+    const T* sin_row = reinterpret_cast<const T*>(p.sin) + (int64_t)n * p.rope_stride_n;
+    const uint4 cl = __ldg(reinterpret_cast<const uint4*>(cos_row + c * 8));
+    const uint4 ch = __ldg(reinterpret_cast<const uint4*>(cos_row + D / 2 + c * 8));
+    const uint4 sl = __ldg(reinterpret_cast<const uint4*>(sin_row + c * 8));
+    const uint4 sh = __ldg(reinterpret_cast<const uint4*>(sin_row + D / 2 + c * 8));
+    const uint32_t clw[4] = {cl.x, cl.y, cl.z, cl.w}, chw[4] = {ch.x, ch.y, ch.z, ch.w};
+    const uint32_t slw[4] = {sl.x, sl.y, sl.z, sl.w}, shw[4] = {sh.x, sh.y, sh.z, sh.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 c1 = tc::Pack2<T>::unpack(clw[i]), c2 = tc::Pack2<T>::unpack(chw[i]);
+      const float2 s1 = tc::Pack2<T>::unpack(slw[i]), s2 = tc::Pack2<T>::unpack(shw[i]);
+      const float a0 = gl[2 * i], a1 = gl[2 * i + 1], b0 = gh[2 * i], b1 = gh[2 * i + 1];
+      // transpose of the rotation, as in the two-pass epilogue
+      gl[2 * i] = a0 * c1.x + b0 * s2.x;     gl[2 * i + 1] = a1 * c1.y + b1 * s2.y;
+      gh[2 * i] = b0 * c2.x - a0 * s1.x;     gh[2 * i + 1] = b1 * c2.y - a1 * s1.y;
+    }
+  }
+  T* dst = reinterpret_cast<T*>(a.dq) + (int64_t)b * a.dq_stride[0] + (int64_t)h * a.dq_stride[1] + (int64_t)n * a.dq_stride[2];
+  uint4 vl, vh;
+  vl.x = tc::Pack2<T>::run(gl[0], gl[1]); vl.y = tc::Pack2<T>::run(gl[2], gl[3]);
+  vl.z = tc::Pack2<T>::run(gl[4], gl[5]); vl.w = tc::Pack2<T>::run(gl[6], gl[7]);
+  vh.x = tc::Pack2<T>::run(gh[0], gh[1]); vh.y = tc::Pack2<T>::run(gh[2], gh[3]);
+  vh.z = tc::Pack2<T>::run(gh[4], gh[5]); vh.w = tc::Pack2<T>::run(gh[6], gh[7]);
+  *reinterpret_cast<uint4*>(dst + c * 8) = vl;
+  *reinterpret_cast<uint4*>(dst + D / 2 + c * 8) = vh;
+}
+
+template <typename T>
+int launch_dq_finish(const float* acc, const AfBwdParams& a, cudaStream_t st) {
+  constexpr int D = 128;
+  const int64_t rows = (int64_t)a.p.B * a.p.H_q * a.p.N_q;
+  const unsigned blocks = (unsigned)((rows * (D / 16) + 255) / 256);
+  if (a.p.rope) bwd_dq_finish_kernel<T, D, true><<<blocks, 256, 0, st>>>(acc, a, rows);
+  else bwd_dq_finish_kernel<T, D, false><<<blocks, 256, 0, st>>>(acc, a, rows);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "bwd_dq_finish launch");
+}
 }  // namespace
+
+// The fused single-pass kernel exists for head_dim 128 (dQ^T is produced with M = head_dim).
+int64_t bwd_mma_dq_accum_bytes(const AfBwdParams& a) {
+  if (a.p.D != 128 || !bwd_mma_supports(a, nullptr)) return 0;
+  return align256(dq_accum_floats(a.p) * 4) + 256;
+}
 
 bool bwd_mma_supports(const AfBwdParams& a, const char** why) {
   const AfProblem& p = a.p;
@@ -71,18 +143,49 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
   if ((rc = tc_make_map(&v128, p.dtype, p.v, p.B, p.H_kv, p.N_kv, p.D, p.v_stride, 128)) != AF_OK) return rc;
   if ((rc = tc_make_map(&q64, p.dtype, q_ptr, p.B, p.H_q, p.N_q, p.D, qs, 64)) != AF_OK) return rc;
   if ((rc = tc_make_map(&do64, p.dtype, a.d_o, p.B, p.H_q, p.N_q, p.D, a.do_stride, 64)) != AF_OK) return rc;
+
+  const int64_t acc_bytes = bwd_mma_dq_accum_bytes(a);
+  if (acc_bytes > 0 && a.dq_accum != nullptr && a.dq_accum_bytes >= acc_bytes && ((uintptr_t)a.dq_accum & 255) == 0) {
+    // ---- single fused pass: dK, dV and dQ from one recompute of S and dP ----
+    tcb::BwdArgs f{};
+    f.a = a;
+    const bool blk = p.mask_kind == AF_MASK_BLOCKS;
+    f.tiles = (p.N_kv + 127) / 128;
+    f.stat_per_block = blk ? p.block_n / 128 : 1;
+    f.steps_per_block = blk ? p.block_m / 64 : 1;
+    const int64_t units = (int64_t)p.B * p.H_kv;
+    AF_REQUIRE((int64_t)f.tiles * units <= 0x7fffffff - 1024, "too many tiles for one launch");
+    f.total_items = (int)(f.tiles * units);
+    int dev = 0, sms = 0;
+    AF_CUDA_OK(cudaGetDevice(&dev));
+    AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    f.grid_ctas = (sms > 0 && sms < f.total_items) ? sms : f.total_items;
+    // Scheduling chunk: as many (batch, kv head) units as keep their dQ accumulator rows (fp32)
+    // and their Q / dO rows inside about half of the L2.
+    const int64_t per_unit = (int64_t)(p.H_q / p.H_kv) * p.N_q * p.D * (4 + 2 + 2);
+    int64_t chunk = (64ll << 20) / (per_unit > 0 ? per_unit : 1);
+    if (const char* env = getenv("ATTNFUSE_BWD_CHUNK")) chunk = atoll(env);
+    if (chunk < 1) chunk = 1;
+    if (chunk > units) chunk = units;
+    f.chunk_units = (int)chunk;
+    f.dq_acc = static_cast<float*>(a.dq_accum);
+    f.sched_counter = reinterpret_cast<int32_t*>(static_cast<char*>(a.dq_accum) + align256(dq_accum_floats(p) * 4));
+    AF_CUDA_OK(cudaMemsetAsync(a.dq_accum, 0, (size_t)acc_bytes, st));
+    if ((rc = tcb::launch_fused_d128(p.dtype, f, k128, v128, q64, do64, st)) != AF_OK) return rc;
+    return p.dtype == AF_F16 ? launch_dq_finish<__half>(f.dq_acc, a, st) : launch_dq_finish<__nv_bfloat16>(f.dq_acc, a, st);
+  }
   if ((rc = tc_make_map(&q128, p.dtype, q_ptr, p.B, p.H_q, p.N_q, p.D, qs, 128)) != AF_OK) return rc;
   if ((rc = tc_make_map(&do128, p.dtype, a.d_o, p.B, p.H_q, p.N_q, p.D, a.do_stride, 128)) != AF_OK) return rc;
   if ((rc = tc_make_map(&k64, p.dtype, k_ptr, p.B, p.H_kv, p.N_kv, p.D, ks, 64)) != AF_OK) return rc;
   if ((rc = tc_make_map(&v64, p.dtype, p.v, p.B, p.H_kv, p.N_kv, p.D, p.v_stride, 64)) != AF_OK) return rc;
 
   const bool blocks = p.mask_kind == AF_MASK_BLOCKS;
-  tcb::BwdArgs dkv;
+  tcb::BwdArgs dkv{};
   dkv.a = a;
   dkv.tiles = (p.N_kv + 127) / 128;
   dkv.stat_per_block = blocks ? p.block_n / 128 : 1;
   dkv.steps_per_block = blocks ? p.block_m / 64 : 1;
-  tcb::BwdArgs dq;
+  tcb::BwdArgs dq{};
   dq.a = a;
   dq.tiles = (p.N_q + 127) / 128;
   dq.stat_per_block = blocks ? p.block_m / 128 : 1;

@@ -80,6 +80,7 @@ int tc_launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t
 int launch_bwd_ffma(const AfBwdParams& a, cudaStream_t st);
 int launch_bwd_delta(const AfBwdParams& a, cudaStream_t st);
 int64_t bwd_mma_workspace_bytes(const AfBwdParams& a);
+int64_t bwd_mma_dq_accum_bytes(const AfBwdParams& a);
 int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st);
 bool bwd_mma_supports(const AfBwdParams& a, const char** why);
 

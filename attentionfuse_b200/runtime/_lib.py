@@ -63,6 +63,7 @@ class AfBwdParams(C.Structure):
         ("dv", PTR), ("dv_stride", S4),
         ("workspace", PTR), ("workspace_bytes", I64),
         ("workspace_holds_rotated", I32),
+        ("dq_accum", PTR), ("dq_accum_bytes", I64),
     ]
 
 
@@ -86,7 +87,7 @@ class AfPeerExchange(C.Structure):
                 ("wait_cycles", I64)]
 
 
-EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_decode_split", "af_decode_combine", "af_decode_static", "af_decode_exchange_bytes", "af_decode_combine_push", "af_decode_wait_merge",
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_bwd_dq_accum_bytes", "af_decode_split", "af_decode_combine", "af_decode_static", "af_decode_exchange_bytes", "af_decode_combine_push", "af_decode_wait_merge",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -115,6 +116,8 @@ def load() -> C.CDLL:
         lib.af_bwd.argtypes = [C.POINTER(AfBwdParams), PTR]
         lib.af_bwd_workspace_bytes.argtypes = [C.POINTER(AfBwdParams)]
         lib.af_bwd_workspace_bytes.restype = I64
+        lib.af_bwd_dq_accum_bytes.argtypes = [C.POINTER(AfBwdParams)]
+        lib.af_bwd_dq_accum_bytes.restype = I64
         lib.af_decode_split.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_combine.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_exchange_bytes.argtypes = [I32, I32, I32, I32]

@@ -9,6 +9,7 @@ bias, cos or sin.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -63,6 +64,13 @@ def launch_backward(Q, K, V, O, L, dO, *, sm_scale, mask_kind, window=0, bias_ki
         else:
             workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
         params.workspace, params.workspace_bytes = workspace.data_ptr(), need
+    # single-pass kernel: dQ is summed over key tiles in an fp32 accumulator (atomic adds, so its
+    # last bits vary from run to run); ATTNFUSE_BWD_DETERMINISTIC=1 keeps the two-pass kernels
+    if os.environ.get("ATTNFUSE_BWD_DETERMINISTIC", "0") != "1":
+        acc_bytes = int(lib.af_bwd_dq_accum_bytes(C.byref(params)))
+        if acc_bytes > 0:
+            dq_accum = torch.empty(acc_bytes, dtype=torch.uint8, device=Q.device)
+            params.dq_accum, params.dq_accum_bytes = dq_accum.data_ptr(), acc_bytes
     with _lib.on_device(Q.device):
         rc = lib.af_bwd(C.byref(params), _lib.current_stream(Q.device))
     _lib.check(rc, "af_bwd")

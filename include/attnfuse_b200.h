@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define AF_ABI_VERSION 2
+#define AF_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define AF_API __attribute__((visibility("default")))
@@ -110,6 +110,13 @@ typedef struct AfBwdParams {
   int32_t workspace_holds_rotated;    /* 1: the workspace already holds the rotated Q and K of
                                          this problem, as af_fwd left them in its own workspace
                                          (same layout); the RoPE pre-pass is then skipped      */
+  void*   dq_accum;                   /* optional scratch of af_bwd_dq_accum_bytes() bytes, 256-byte
+                                         aligned: an fp32 (B, H_q, N_q, D) accumulator for dQ.  With
+                                         it af_bwd runs the single-pass kernel (S and dP computed
+                                         once, dQ summed over key tiles with fp32 atomic adds, so
+                                         its last bits depend on scheduling); without it the
+                                         deterministic two-pass kernels run                    */
+  int64_t dq_accum_bytes;
 } AfBwdParams;
 
 /* Split-K decode (query length 1).  Workspaces are fp32:
@@ -157,6 +164,13 @@ AF_API int af_bwd(const AfBwdParams* params, af_stream_t stream);
 /* Scratch bytes the tensor-core backward needs for this problem (0: none).  RoPE problems keep
  * the rotated Q and K there; without it af_bwd runs the exact FFMA kernels.  Host only. */
 AF_API int64_t af_bwd_workspace_bytes(const AfBwdParams* params);
+
+/* Bytes of the optional dQ accumulator (AfBwdParams.dq_accum) with which af_bwd runs its
+ * single-pass kernel for this problem; 0 when only the two-pass kernels apply (head_dim other than
+ * 128, fp32, additive bias, ...).  af_bwd clears the accumulator itself.  No counterpart in the
+ * reference, whose backward always recomputes S and dP in both of its kernels
+ * (attnfuse/compiler/codegen_backward.py:75-302).  Host only. */
+AF_API int64_t af_bwd_dq_accum_bytes(const AfBwdParams* params);
 
 /* Replaces the split launch of run_flash_decode (attnfuse/runtime/flash_decode.py:149-170). */
 AF_API int af_decode_split(const AfDecodeParams* params, af_stream_t stream);

@@ -26,7 +26,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(_lib.EXPORTS) == names
-    assert lib.af_abi_version() == 2
+    assert lib.af_abi_version() == 3
     assert lib.af_launch_count() >= 0
 
 

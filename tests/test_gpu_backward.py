@@ -148,6 +148,43 @@ def test_backward_tcgen05_longer(variant, shape):
     check(variant, shape, torch.bfloat16)
 
 
+@pytest.mark.parametrize("variant", ["dense", "causal", "causal_rope", "causal_alibi", "window"])
+@pytest.mark.parametrize("shape", [(1, 8, 2, 1024, 128), (2, 2, 1, 333, 128), (1, 4, 4, 64, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_two_pass_and_single_pass_kernels_agree(variant, shape, monkeypatch):
+    """Head dim 128 runs the single-pass kernel by default (dQ summed over key tiles in an fp32
+    accumulator with atomic adds); ATTNFUSE_BWD_DETERMINISTIC=1 keeps the two-pass kernels.  Both
+    meet the bar against the oracle, the two-pass result is bit-reproducible, and the two differ
+    by rounding only."""
+    B, Hq, Hkv, N, D = shape
+    dtype = torch.bfloat16
+    Q, K, V = qkv(1500, B, Hq, Hkv, N, N, D, dtype)
+    dO = orc.randn(1503, (B, Hq, N, D), dtype)
+    kw, okw = {}, {"causal": variant.startswith("causal")}
+    fn = {"dense": dense, "causal": causal, "causal_rope": causal_rope, "causal_alibi": make_causal_alibi(Hq),
+          "window": make_window(100)}[variant]
+    if variant == "causal_rope":
+        cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
+        kw.update(cos=cos.to(DEV), sin=sin.to(DEV)); okw.update(cos=cos, sin=sin)
+    if variant == "causal_alibi":
+        okw["slopes"] = _alibi_slopes(Hq, "cpu", str(dtype))
+    if variant == "window":
+        okw["window"] = 100
+    O, dQ, dK, dV = orc.attention_grads(Q, K, V, dO, **okw)
+    before = _lib.launch_count()
+    _, dq1, dk1, dv1 = grads(fn, Q, K, V, dO, **kw)
+    single_pass_launches = _lib.launch_count() - before
+    monkeypatch.setenv("ATTNFUSE_BWD_DETERMINISTIC", "1")
+    _, dq2, dk2, dv2 = grads(fn, Q, K, V, dO, **kw)
+    _, dq3, dk3, dv3 = grads(fn, Q, K, V, dO, **kw)
+    assert torch.equal(dq2, dq3) and torch.equal(dk2, dk3) and torch.equal(dv2, dv3)
+    for name, got1, got2, want in (("dQ", dq1, dq2, dQ), ("dK", dk1, dk2, dK), ("dV", dv1, dv2, dV)):
+        assert_close(got1, want, dtype, grad=True, what=f"single-pass {variant} {name}")
+        assert_close(got2, want, dtype, grad=True, what=f"two-pass {variant} {name}")
+        assert orc.rel_fro(got1.float().cpu(), got2.float().cpu()) < 1e-2
+    assert single_pass_launches >= 4      # forward (+ rotation), delta, fused pass, dQ finish
+
+
 @pytest.mark.parametrize("window", [1, 64, 200, 513])
 @pytest.mark.parametrize("D", [64, 128])
 def test_window_backward_on_tensor_cores(window, D):
