@@ -171,8 +171,23 @@ int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv,
     };
     want = fill(s2) > fill(s1) + 1e-9 ? s2 : s1;
   } else {
-    const int64_t slots = 2LL * sm_count * 5;
-    want = (slots + units - 1) / units;
+    const int64_t slots = 2LL * sm_count;          // CTAs resident at once
+    want = (5 * slots + units - 1) / units;
+    // Whole waves: with equal-length sequences every CTA takes the same time, so a last wave that
+    // fills a fifth of the slots costs as much as a full one.  Among the split counts around the
+    // five-wave target take the one whose last wave is fullest.
+    const int64_t cap0 = N_kv / 512 > 1 ? N_kv / 512 : 1;
+    const int64_t hi = (want * 3 / 2 < cap0 ? want * 3 / 2 : cap0) < 64 ? (want * 3 / 2 < cap0 ? want * 3 / 2 : cap0) : 64;
+    const int64_t lo = want * 3 / 4 > 1 ? want * 3 / 4 : 1;
+    double best = -1.0;
+    int64_t pick = want;
+    for (int64_t s = lo; s <= hi; ++s) {
+      const int64_t ctas = units * s, waves = (ctas + slots - 1) / slots;
+      const double fill = (double)ctas / (double)(waves * slots);
+      const int64_t dist = s > want ? s - want : want - s, best_dist = pick > want ? pick - want : want - pick;
+      if (fill > best + 1e-9 || (fill > best - 1e-9 && dist < best_dist)) { best = fill; pick = s; }
+    }
+    if (hi >= lo) want = pick;
   }
   const int64_t cap = N_kv / 512 > 1 ? N_kv / 512 : 1;
   if (want > cap) want = cap;

@@ -161,9 +161,10 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
     AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     f.grid_ctas = (sms > 0 && sms < f.total_items) ? sms : f.total_items;
     // Scheduling chunk: as many (batch, kv head) units as keep their dQ accumulator rows (fp32)
-    // and their Q / dO rows inside about half of the L2.
+    // and their Q / dO rows inside the L2 (measured at B4 H32/8 N4096: 2 units 2.30 ms, 3: 2.25,
+    // 8: 2.24, all 32: 2.37 for the whole training step).
     const int64_t per_unit = (int64_t)(p.H_q / p.H_kv) * p.N_q * p.D * (4 + 2 + 2);
-    int64_t chunk = (64ll << 20) / (per_unit > 0 ? per_unit : 1);
+    int64_t chunk = (128ll << 20) / (per_unit > 0 ? per_unit : 1);
     if (const char* env = getenv("ATTNFUSE_BWD_CHUNK")) chunk = atoll(env);
     if (chunk < 1) chunk = 1;
     if (chunk > units) chunk = units;

@@ -11,7 +11,11 @@ import threading
 from pathlib import Path
 from typing import Optional, Sequence
 
-LIB_PATH = Path(__file__).resolve().parent.parent / "csrc" / "libattnfuse_b200.so"
+import os
+
+# ATTNFUSE_B200_LIBRARY points at a build of the library kept somewhere else
+LIB_PATH = Path(os.environ.get("ATTNFUSE_B200_LIBRARY") or
+                Path(__file__).resolve().parent.parent / "csrc" / "libattnfuse_b200.so")
 
 AF_F16, AF_BF16, AF_F32 = 0, 1, 2
 AF_MASK_FULL, AF_MASK_CAUSAL, AF_MASK_WINDOW, AF_MASK_BLOCKS = 0, 1, 2, 3

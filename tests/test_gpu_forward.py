@@ -238,8 +238,9 @@ def test_lse_output():
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_rope_prepass_and_in_kernel_rotation_agree(D, dtype, monkeypatch):
     """Long sequences rotate Q and K once in a pre-pass (caller workspace); short ones, or callers
-    that pass no workspace, rotate inside the kernel in shared memory.  Same arithmetic, same bits."""
-    B, Hq, Hkv, N = 1, 8, 2, 1000
+    that pass no workspace, rotate inside the kernel in shared memory.  Same arithmetic, same bits.
+    Several query tiles per CTA, so that the persistent pipeline crosses item boundaries."""
+    B, Hq, Hkv, N = 3, 16, 4, 1000
     Q, K, V = qkv(900, B, Hq, Hkv, N, N, D, dtype)
     cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
     q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
