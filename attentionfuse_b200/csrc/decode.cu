@@ -76,8 +76,31 @@ __device__ __forceinline__ uint32_t tile_off(int r, int c) {
   return (uint32_t)(r * ROW_BYTES + (((c & ~7) | ((c ^ r) & 7)) << 4));
 }
 
+// Unpack / pack two elements of T.
+template <typename T> struct Pair;
+template <> struct Pair<__half> {
+  __device__ __forceinline__ static float2 unpack(uint32_t x) { return __half22float2(*reinterpret_cast<__half2*>(&x)); }
+};
+template <> struct Pair<__nv_bfloat16> {
+  __device__ __forceinline__ static float2 unpack(uint32_t x) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&x)); }
+};
+
+// Rotate-half on two packed pairs: (lo, hi) are elements (d, d+1) and (d + D/2, d + D/2 + 1);
+// fp32 math, one rounding to T -- the rounding point of the forward kernels.
+template <typename T>
+__device__ __forceinline__ void rotate_words(uint32_t& lo, uint32_t& hi, uint32_t c_lo, uint32_t c_hi, uint32_t s_lo,
+                                             uint32_t s_hi) {
+  const float2 x1 = Pair<T>::unpack(lo), x2 = Pair<T>::unpack(hi);
+  const float2 c1 = Pair<T>::unpack(c_lo), c2 = Pair<T>::unpack(c_hi);
+  const float2 s1 = Pair<T>::unpack(s_lo), s2 = Pair<T>::unpack(s_hi);
+  lo = MmaOp<T>::pack(x1.x * c1.x - x2.x * s1.x, x1.y * c1.y - x2.y * s1.y);
+  hi = MmaOp<T>::pack(x2.x * c2.x + x1.x * s2.x, x2.y * c2.y + x1.y * s2.y);
+}
+
 // KPW = keys of each 64-key tile one warp handles (16: warps split keys; 64: warps split heads).
-template <typename T, int D, int KPW>
+// ROPE: the query row is rotated in registers at its position, every K tile in place in shared
+// memory at the keys' positions, before the dot.
+template <typename T, int D, int KPW, bool ROPE>
 __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks) {
   constexpr int ROW_BYTES = D * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;       // 16-byte chunks per row
@@ -104,10 +127,21 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
   const int key_w0 = SPLIT_KEYS ? warp * 16 : 0;   // first key of the tile this warp handles
 
   const int len_b = a.kv_lens ? min(max(a.kv_lens[b], 0), a.N_kv) : a.N_kv;
-  int split_len = (len_b + a.num_splits - 1) / a.num_splits;
+  // Position of the query row on the key axis.  ALiBi measures its distance from there (the
+  // reference uses the last key, attnfuse/compiler/codegen_decode.py:142-145); the causal and
+  // window masks of a single row are a range of keys.
+  const int q_pos = a.q_positions ? a.q_positions[b] : (a.q_position_p1 > 0 ? a.q_position_p1 - 1 : a.kv_offset + len_b - 1);
+  int k_lo = 0, k_hi = len_b;
+  if (a.mask_kind == AF_MASK_CAUSAL) k_hi = min(k_hi, q_pos - a.kv_offset + 1);
+  if (a.mask_kind == AF_MASK_WINDOW) {
+    k_lo = max(0, q_pos - a.window + 1 - a.kv_offset);
+    k_hi = min(k_hi, q_pos + a.window - a.kv_offset);
+  }
+  const int span = max(k_hi - k_lo, 0);
+  int split_len = (span + a.num_splits - 1) / a.num_splits;
   split_len = ((split_len + DEC_BN - 1) / DEC_BN) * DEC_BN;
-  const int lo = split * split_len;
-  const int hi = min(lo + split_len, len_b);
+  const int lo = k_lo + split * split_len;
+  const int hi = min(lo + split_len, k_lo + span);
   const int n_tiles = hi > lo ? (hi - lo + DEC_BN - 1) / DEC_BN : 0;
 
   const T* kbase = reinterpret_cast<const T*>(a.k) + (int64_t)b * a.k_stride[0] + (int64_t)h_kv * a.k_stride[1];
@@ -145,6 +179,22 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
     }
   }
 
+  if (ROPE) {
+    // elements d (k-step kk) pair with d + D/2 (k-step kk + KSTEPS/2), same register slot
+    const T* cr = reinterpret_cast<const T*>(a.cos) + (int64_t)q_pos * a.rope_stride_n;
+    const T* sr = reinterpret_cast<const T*>(a.sin) + (int64_t)q_pos * a.rope_stride_n;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS / 2; ++kk) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int d = kk * 16 + 2 * t + (r >> 1) * 8;
+        rotate_words<T>(qf[kk][r], qf[kk + KSTEPS / 2][r], *reinterpret_cast<const uint32_t*>(cr + d),
+                        *reinterpret_cast<const uint32_t*>(cr + d + D / 2), *reinterpret_cast<const uint32_t*>(sr + d),
+                        *reinterpret_cast<const uint32_t*>(sr + d + D / 2));
+      }
+    }
+  }
+
   const float scale2 = a.sm_scale * kLog2e;
   float slope2[2] = {0.f, 0.f};
   if (a.bias_kind == AF_BIAS_ALIBI) {
@@ -152,10 +202,6 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
     if (hl0 < group) slope2[0] = load_slope<T>(a.slopes, h_kv * group + hl0) * kLog2e;
     if (hl1 < group) slope2[1] = load_slope<T>(a.slopes, h_kv * group + hl1) * kLog2e;
   }
-  // ALiBi distance is measured from the query position: the last valid key
-  // (attnfuse/compiler/codegen_decode.py:142-145 uses N_KV - 1).
-  const int q_pos = a.q_positions ? a.q_positions[b] : (a.kv_offset + len_b - 1);
-
   float m2[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[NT_O][4];
 #pragma unroll
@@ -178,6 +224,28 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
     const int slot = tile % DEC_STAGES;
     const uint32_t kt = smem_u32(sK + slot * TILE_BYTES);
     const uint32_t vt = smem_u32(sV + slot * TILE_BYTES);
+    if (ROPE) {
+      // rotate the K tile in place: a thread takes pairs of 16-byte chunks (c, c + CHUNKS/2) of a row
+      const int key0 = lo + tile * DEC_BN;
+      for (int i = tid; i < DEC_BN * (CHUNKS / 2); i += DEC_THREADS) {
+        const int r = i / (CHUNKS / 2), c = i - r * (CHUNKS / 2);
+        if (key0 + r >= hi) continue;
+        const int64_t tab = (int64_t)(a.kv_offset + key0 + r) * a.rope_stride_n + c * 8;
+        const uint4 cl = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.cos) + tab));
+        const uint4 ch = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.cos) + tab + D / 2));
+        const uint4 sl = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.sin) + tab));
+        const uint4 sh = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.sin) + tab + D / 2));
+        uint4* pl = reinterpret_cast<uint4*>(sK + slot * TILE_BYTES + tile_off<D>(r, c));
+        uint4* ph = reinterpret_cast<uint4*>(sK + slot * TILE_BYTES + tile_off<D>(r, c + CHUNKS / 2));
+        uint4 xl = *pl, xh = *ph;
+        rotate_words<T>(xl.x, xh.x, cl.x, ch.x, sl.x, sh.x);
+        rotate_words<T>(xl.y, xh.y, cl.y, ch.y, sl.y, sh.y);
+        rotate_words<T>(xl.z, xh.z, cl.z, ch.z, sl.z, sh.z);
+        rotate_words<T>(xl.w, xh.w, cl.w, ch.w, sl.w, sh.w);
+        *pl = xl; *ph = xh;
+      }
+      __syncthreads();
+    }
     const int key_base = lo + tile * DEC_BN + key_w0;   // first key this warp sees in the tile
     if (SPLIT_KEYS && key_base >= hi) continue;         // warp-uniform: nothing valid here
 
@@ -401,15 +469,18 @@ int launch_split_impl(const AfDecodeParams& a, cudaStream_t st) {
   const int head_chunks = (group + 63) / 64;
   const size_t smem = (size_t)2 * DEC_STAGES * DEC_BN * D * 2;
   dim3 grid(a.num_splits, a.B * a.H_kv * head_chunks);
+#define AF_DECODE_LAUNCH(KPW, ROPE)                                                                        \
+  do {                                                                                                    \
+    auto kern = decode_split_kernel<T, D, KPW, ROPE>;                                                     \
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);                                                \
+  } while (0)
   if (group <= 16) {
-    auto kern = decode_split_kernel<T, D, 16>;
-    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);
+    if (a.rope) AF_DECODE_LAUNCH(16, true); else AF_DECODE_LAUNCH(16, false);
   } else {
-    auto kern = decode_split_kernel<T, D, 64>;
-    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);
+    if (a.rope) AF_DECODE_LAUNCH(64, true); else AF_DECODE_LAUNCH(64, false);
   }
+#undef AF_DECODE_LAUNCH
   count_launch();
   return check_cuda(cudaGetLastError(), "decode_split launch");
 }
@@ -475,7 +546,7 @@ int launch_decode_static(const AfDecodeParams& in, cudaStream_t st) {
     int dev = 0, sms = 0;
     AF_CUDA_OK(cudaGetDevice(&dev));
     AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    a.num_splits = af_decode_num_splits(a.B, a.H_q, a.H_kv, a.N_kv, sms);
+    a.num_splits = af_decode_num_splits(a.B, a.H_q, a.H_kv, a.N_kv, sms, a.kv_lens != nullptr);
   }
   AF_REQUIRE(a.B > 0 && a.H_q > 0 && a.D > 0, "bad sizes");
   AF_REQUIRE(a.o || a.partial, "combine needs o or partial");
@@ -514,6 +585,13 @@ int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
              "decode needs 16-byte aligned K/V base pointers");
   AF_REQUIRE(a.q_stride[1] % 2 == 0 && a.q_stride[0] % 2 == 0, "decode needs 4-byte aligned Q rows");
   AF_REQUIRE(a.bias_kind == AF_BIAS_NONE || (a.bias_kind == AF_BIAS_ALIBI && a.slopes), "bad bias_kind for decode");
+  AF_REQUIRE(a.mask_kind == AF_MASK_FULL || a.mask_kind == AF_MASK_CAUSAL || (a.mask_kind == AF_MASK_WINDOW && a.window > 0),
+             "decode takes full, causal or window masks (mask_kind %d, window %d)", a.mask_kind, a.window);
+  if (a.rope) {
+    AF_REQUIRE(a.cos && a.sin, "RoPE decode needs cos and sin tables");
+    AF_REQUIRE(a.rope_stride_n % 8 == 0 && ((uintptr_t)a.cos & 15) == 0 && ((uintptr_t)a.sin & 15) == 0,
+               "cos/sin rows must be 16-byte aligned");
+  }
   // more than 16 query heads per KV head: tensor-bound on mma.sync, so the tcgen05 kernel takes it
   if (decode_tc_supports(a)) return launch_decode_split_tc(a, st);
   if (a.dtype == AF_F16) return a.D == 64 ? launch_split_impl<__half, 64>(a, st) : launch_split_impl<__half, 128>(a, st);

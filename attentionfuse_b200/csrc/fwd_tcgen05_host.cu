@@ -272,6 +272,7 @@ bool decode_tc_supports(const AfDecodeParams& a) {
   if (a.dtype != AF_F16 && a.dtype != AF_BF16) return false;
   if (a.D != 64 && a.D != 128) return false;
   if (a.bias_kind != AF_BIAS_NONE || !(a.sm_scale > 0.f) || a.N_kv < 1 || a.num_splits < 1) return false;
+  if (a.mask_kind != AF_MASK_FULL || a.rope) return false;   // masks and rotation: the mma.sync kernel
   if (a.ws_acc == nullptr || ((uintptr_t)a.ws_acc & 15) != 0) return false;
   int64_t qs[4];
   decode_q_view(a, qs);

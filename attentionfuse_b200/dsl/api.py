@@ -120,7 +120,8 @@ def attention(fn: Callable) -> Callable:
         if _wants_grad(Q, K, V):
             from ..runtime.backward import can_backward
             # a query position offset (chunked prefill against a cache) is forward only
-            if can_backward(graph) and not kwargs.get("q_offset"):
+            off = kwargs.get("q_offset")
+            if can_backward(graph) and (off is None or (isinstance(off, int) and off == 0)):
                 from ..runtime.autograd import AttnFuseFunction
                 return AttnFuseFunction.apply(graph, Q, K, V, bias, cos, sin)
             # No backward for this composition: run inference, no gradient flows.

@@ -83,6 +83,8 @@ class AfDecodeParams(C.Structure):
         ("ws_m", PTR), ("ws_l", PTR), ("ws_acc", PTR),
         ("o", PTR), ("o_stride", S4),
         ("partial", PTR), ("status", PTR),
+        ("mask_kind", I32), ("window", I32), ("rope", I32), ("q_position_p1", I32),
+        ("cos", PTR), ("sin", PTR), ("rope_stride_n", I64),
     ]
 
 
@@ -133,7 +135,7 @@ def load() -> C.CDLL:
         lib.af_decode_static.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_static.restype = I32
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
-        lib.af_decode_num_splits.argtypes = [I32, I32, I32, I32, I32]
+        lib.af_decode_num_splits.argtypes = [I32, I32, I32, I32, I32, I32]
         lib.af_query_family.argtypes = [C.POINTER(AfProblem), I32]
         for name in ("af_fwd", "af_bwd", "af_decode_split", "af_decode_combine",
                      "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",

@@ -143,15 +143,37 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
     validate_qkv(Q, K, V)
     N_q, N_kv = Q.shape[2], K.shape[2]
     bundle = get_or_compile(graph)
+    q_positions = None
+    if isinstance(q_offset, torch.Tensor):
+        # per-sequence positions of a single query row (decoding a ragged batch)
+        if N_q != 1 or q_offset.shape != (Q.shape[0],):
+            raise ValueError("a tensor q_offset gives one position per batch entry and needs query length 1")
+        q_positions, q_offset = q_offset, None
     if q_offset is not None and (not isinstance(q_offset, int) or q_offset < 0):
-        raise ValueError(f"q_offset must be a non-negative int; got {q_offset!r}")
+        raise ValueError(f"q_offset must be a non-negative int or an int32 tensor (B,); got {q_offset!r}")
 
     from .flash_decode import can_use_flash_decode, run_flash_decode
-    if save_lse is None and not q_offset and can_use_flash_decode(graph, Q, K):
+    positioned = q_offset is not None or q_positions is not None
+    if save_lse is None and can_use_flash_decode(graph, Q, K, positioned):
         if out is None:
             out = torch.empty_like(Q)
+        c = s = None
+        if bundle.has_rope:
+            if cos is None or sin is None:
+                raise RuntimeError(
+                    "This attention graph was built with af.rope(); you must pass cos=<table> "
+                    "and sin=<table> at call time.")
+            c, s = _rope_table(cos, "cos", Q), _rope_table(sin, "sin", Q)
+            if c.shape[1] != Q.shape[3] or s.shape != c.shape or c.shape[0] < N_kv or (
+                    q_offset is not None and c.shape[0] <= q_offset) or c.stride(0) != s.stride(0):
+                raise ValueError(f"cos/sin tables must cover every key and the query position; got {tuple(c.shape)}")
         return run_flash_decode(graph, Q, K, V, bundle.sm_scale, bundle.bias_kind, K.shape[1], out,
-                                kv_lens=kv_lens, alibi_slopes=alibi_slopes)
+                                kv_lens=kv_lens, alibi_slopes=alibi_slopes, q_positions=q_positions,
+                                q_position=q_offset, mask_kind=bundle.mask_kind, window=bundle.window,
+                                cos=c, sin=s)
+    if q_positions is not None:
+        raise ValueError("per-sequence query positions are only supported on the flash-decoding path "
+                         "(query length 1, f16/bf16, head_dim 64/128, N_kv >= 256)")
     if kv_lens is not None:
         raise ValueError("kv_lens is only supported on the flash-decoding path "
                          "(query length 1, f16/bf16, head_dim 64/128, N_kv >= 256)")

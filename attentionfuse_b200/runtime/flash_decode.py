@@ -21,14 +21,19 @@ DECODE_HEAD_DIMS = (64, 128)
 DECODE_DTYPES = (torch.float16, torch.bfloat16)
 
 
-def can_use_flash_decode(graph: Graph, Q: torch.Tensor, K: torch.Tensor) -> bool:
+def can_use_flash_decode(graph: Graph, Q: torch.Tensor, K: torch.Tensor, positioned: bool = False) -> bool:
+    """The reference's rule (query length 1, N_kv >= 256, dense or ALiBi, no RoPE:
+    attnfuse/runtime/flash_decode.py:46-65).  With ``positioned`` -- the caller said where the
+    query row sits on the key axis -- causal and sliding-window masks and RoPE are taken too:
+    for a single row a mask is a range of keys, and the kernel rotates the row and the key tiles."""
     if Q.shape[2] != 1 or K.shape[2] < 256:
         return False
-    if {m.kind for m in graph.collect_masks()} - {MaskKind.FULL}:
+    allowed_masks = {MaskKind.FULL, MaskKind.CAUSAL, MaskKind.SLIDING_WINDOW} if positioned else {MaskKind.FULL}
+    if {m.kind for m in graph.collect_masks()} - allowed_masks:
         return False
     if {b.kind for b in graph.collect_biases()} - {BiasKind.ALIBI}:
         return False
-    if graph.has_rope():
+    if graph.has_rope() and not positioned:
         return False
     # The mma.sync decode kernels are instantiated for these types and head dims; anything
     # else takes the general forward kernel (N_q = 1 is a legal dense problem there).
@@ -46,9 +51,9 @@ def _sm_count(device_index: int) -> int:
     return torch.cuda.get_device_properties(device_index).multi_processor_count
 
 
-def _pick_num_splits(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int = 0) -> int:
+def _pick_num_splits(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int = 0, ragged: bool = False) -> int:
     """Split count (stands in for attnfuse/runtime/flash_decode.py:69-95)."""
-    return int(_lib.load().af_decode_num_splits(B, H_q, H_kv, N_kv, _sm_count(device_index)))
+    return int(_lib.load().af_decode_num_splits(B, H_q, H_kv, N_kv, _sm_count(device_index), int(ragged)))
 
 
 def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device):
@@ -67,7 +72,9 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      alibi_slopes: Optional[torch.Tensor] = None, kv_offset: int = 0,
                      q_positions: Optional[torch.Tensor] = None,
                      partial: Optional[torch.Tensor] = None,
-                     num_splits: Optional[int] = None, workspace=None, exchange=None) -> torch.Tensor:
+                     num_splits: Optional[int] = None, workspace=None, exchange=None,
+                     mask_kind: int = 0, window: int = 0, q_position: Optional[int] = None,
+                     cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
     when only the packed partial is requested)."""
     lib = _lib.load()
@@ -77,7 +84,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         V = V.contiguous()
     dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     if num_splits is None:
-        num_splits = _pick_num_splits(B, H_q, H_kv, N_kv, dev_index)
+        num_splits = _pick_num_splits(B, H_q, H_kv, N_kv, dev_index, kv_lens is not None)
     ws_m, ws_l, ws_acc = workspace if workspace is not None else decode_workspace(
         num_splits, B, H_q, D, Q.device)
 
@@ -103,6 +110,11 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     p.v, p.v_stride = V.data_ptr(), _lib.strides(V)
     p.slopes, p.kv_lens, p.q_positions = _lib.ptr(slopes), _lib.ptr(kv_lens), _lib.ptr(q_positions)
     p.kv_offset = int(kv_offset)
+    p.mask_kind, p.window = int(mask_kind), int(window or 0)
+    if q_position is not None:
+        p.q_position_p1 = int(q_position) + 1
+    if cos is not None:
+        p.rope, p.cos, p.sin, p.rope_stride_n = 1, cos.data_ptr(), sin.data_ptr(), cos.stride(0)
     p.ws_m, p.ws_l, p.ws_acc = ws_m.data_ptr(), ws_l.data_ptr(), ws_acc.data_ptr()
     if out is not None:
         p.o, p.o_stride = out.data_ptr(), _lib.strides(out)

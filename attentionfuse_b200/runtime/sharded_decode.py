@@ -201,7 +201,7 @@ class ShardedDecodePlan:
         self.slopes = None if slopes is None else slopes.to(device=device, dtype=dtype).contiguous()
         index = device.index if getattr(device, "index", None) is not None else torch.cuda.current_device()
         self.kv_offset = self.lo if layout == "contiguous" else 0
-        self.num_splits = _pick_num_splits(B, H_q, H_kv, max(self.hi - self.lo, 1), index)
+        self.num_splits = _pick_num_splits(B, H_q, H_kv, max(self.hi - self.lo, 1), index, kv_lens is not None)
         self.workspace = decode_workspace(self.num_splits, B, H_q, D, device)
         self.partial = torch.empty(B, H_q, D + 1, dtype=torch.float32, device=device)
         self.gathered = torch.empty(world, B, H_q, D + 1, dtype=torch.float32, device=device)

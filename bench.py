@@ -486,7 +486,7 @@ def sweep(which: str):
                 out = torch.empty_like(Q)
                 it = [0]
 
-                S = _pick_num_splits(B, Hq, Hkv, L, 0)
+                S = _pick_num_splits(B, Hq, Hkv, L, 0, True)
                 ws = decode_workspace(S, B, Hq, D, dev)   # allocated once, as a serving loop would
 
                 def step():
@@ -497,6 +497,24 @@ def sweep(which: str):
                 gbs = nbytes / (ms * 1e-3) / 1e9
                 print(json.dumps({"sweep": "cfg3", "H_q": Hq, "H_kv": Hkv, "L": L, "ms": round(ms, 4),
                                   "num_splits": S, "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}), flush=True)
+                if L == 32768 and Hkv == 8:
+                    # one query row at the end of each sequence with a mask / rotation: the same
+                    # split-K kernels, the mask as a range of keys, RoPE on the tiles in shared memory
+                    cos, sin = (t.to(dev) for t in orc.build_rope_cache(L, D, 500000.0, dt))
+                    pos = lens - 1
+                    for name, mask_kind, window, rope in (("causal", 1, 0, False), ("window4096", 2, 4096, False),
+                                                          ("causal+rope", 1, 0, True)):
+                        def step_masked():
+                            Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
+                            run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens, num_splits=S,
+                                             workspace=ws, q_positions=pos, mask_kind=mask_kind, window=window,
+                                             cos=cos if rope else None, sin=sin if rope else None)
+                        ms = _median_ms(step_masked)
+                        keys = float(torch.clamp(lens, max=window).sum().item()) if mask_kind == 2 else float(lens.sum().item())
+                        nb = 2.0 * Hkv * D * 2 * keys + 2.0 * B * Hq * D * 2
+                        print(json.dumps({"sweep": "cfg3", "single_row": name, "H_q": Hq, "H_kv": Hkv, "L": L,
+                                          "ms": round(ms, 4), "gbs": round(nb / (ms * 1e-3) / 1e9, 1),
+                                          "frac_of_measured_hbm": round(nb / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)}), flush=True)
                 del caches
     else:
         B, H, N, D, blk, dt = 2, 16, 8192, 64, 128, torch.float16
@@ -592,7 +610,7 @@ def bench_decode(dev, rank, world, dist_on, pk):
     Q = torch.randn(B, Hq, 1, D, generator=gen, device=dev, dtype=dt)
     out = torch.empty_like(Q)
     lens_d = lens.to(dev)
-    S = _pick_num_splits(B, Hq, Hkv, L, dev.index or 0)
+    S = _pick_num_splits(B, Hq, Hkv, L, dev.index or 0, True)
     ws = decode_workspace(S, B, Hq, D, dev)
     sm_scale = 1.0 / D ** 0.5
     bytes_step = 2.0 * Hkv * D * 2 * float(lens.sum()) + 2.0 * B * Hq * D * 2

@@ -142,6 +142,19 @@ typedef struct AfDecodeParams {
   void*  o; int64_t o_stride[4];  /* (B, H_q, 1, D) final output, or NULL                 */
   float* partial;               /* optional [B, H_q, D+1] fp32: normalised O then LSE      */
   int32_t* status;
+  /* The single query row of batch entry b sits at position q_pos[b] of the key axis:
+   * q_positions[b] if given, else q_position_p1 - 1 if q_position_p1 > 0, else
+   * kv_offset + (valid keys) - 1.
+   * ALiBi measures its distance from there; AF_MASK_CAUSAL keeps keys at positions <= q_pos,
+   * AF_MASK_WINDOW keys with |q_pos - position| < window; rope = 1 rotates the query at q_pos
+   * and every key at its own position (rotate-half, tables as in AfProblem) before the dot.
+   * None of these exists in the reference, whose decode path takes dense and ALiBi graphs
+   * only (attnfuse/runtime/flash_decode.py:46-65).  Zero-initialised fields give the
+   * reference's behaviour. */
+  int32_t mask_kind, window;
+  int32_t rope;
+  int32_t q_position_p1;        /* query position + 1; 0 = not given                        */
+  const void* cos; const void* sin; int64_t rope_stride_n;
 } AfDecodeParams;
 
 /* Replaces the forward launch in run_attention (attnfuse/runtime/dispatch.py:196-214)
@@ -241,8 +254,12 @@ AF_API int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32
                                 af_stream_t stream);
 
 /* Split count for a decode problem: the reference's _pick_num_splits
- * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  Host only. */
-AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count);
+ * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  `ragged` != 0: the
+ * sequences have different valid lengths (kv_lens), so the CTAs of a launch take different
+ * times and about five waves of them even out; 0: equal lengths, where the count is chosen so
+ * that the last wave of resident CTAs is as full as possible.  Host only. */
+AF_API int32_t af_decode_num_splits(int32_t B, int32_t H_q, int32_t H_kv, int32_t N_kv, int32_t sm_count,
+                                    int32_t ragged);
 
 /* Which family af_fwd / af_bwd would run for this problem (AF_FAMILY_*), or a negative
  * error.  Host only; stands in for the reference's tile-table lookup

@@ -51,11 +51,12 @@ def test_struct_layouts_match_the_header(tmp_path):
 
 def test_host_only_entry_points():
     lib = _lib.load()
-    assert lib.af_decode_num_splits(16, 32, 8, 32768, 148) == 16     # 2048 CTAs = 6.9 waves of 296 slots (12 would leave a fifth-full sixth wave)
-    assert lib.af_decode_num_splits(16, 64, 1, 32768, 148) == 9      # MQA: one item per SM of the persistent kernel
-    assert lib.af_decode_num_splits(1, 8, 8, 32768, 148) == 64       # capped
-    assert lib.af_decode_num_splits(1, 1, 1, 300, 148) == 1          # fewer than 512 keys per split
-    assert lib.af_decode_num_splits(16, 32, 8, 4096, 148) == 8
+    assert lib.af_decode_num_splits(16, 32, 8, 32768, 148, 1) == 12    # ragged lengths: 1480 CTA slots / 128 units
+    assert lib.af_decode_num_splits(16, 32, 8, 32768, 148, 0) == 16    # equal lengths: 2048 CTAs = 6.9 waves of 296 slots
+    assert lib.af_decode_num_splits(16, 64, 1, 32768, 148, 0) == 9     # MQA: one item per SM of the persistent kernel
+    assert lib.af_decode_num_splits(1, 8, 8, 32768, 148, 0) == 64      # capped
+    assert lib.af_decode_num_splits(1, 1, 1, 300, 148, 0) == 1         # fewer than 512 keys per split
+    assert lib.af_decode_num_splits(16, 32, 8, 4096, 148, 1) == 8
     # invalid arguments are refused on the host, before any CUDA call
     params = _lib.AfFwdParams()
     params.p.dtype = 7

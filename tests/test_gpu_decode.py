@@ -91,6 +91,68 @@ def test_odd_partial_row_counts(heads, splits, B):
         assert_close(dense(q, k, v), orc.attention(Q, K, V), torch.bfloat16, what=f"odd rows auto {heads} B={B}")
 
 
+def build_graph(variant, H, W):
+    @af.attention
+    def fn(Q, K, V):
+        s = af.rope(Q, K) if "rope" in variant else af.scaled_dot_product(Q, K)
+        if "alibi" in variant:
+            s = af.alibi(s, H)
+        if "causal" in variant:
+            s = af.causal(s)
+        if "window" in variant:
+            s = af.sliding_window(s, W)
+        return af.softmax(s) @ V
+    return fn
+
+
+@pytest.mark.parametrize("variant", ["causal", "window", "causal_alibi", "causal_rope", "causal_rope_alibi", "window_rope"])
+@pytest.mark.parametrize("geom", [(32, 8, 128), (64, 1, 128), (8, 2, 64)], ids=lambda g: f"{g[0]}q{g[1]}kv_d{g[2]}")
+def test_single_row_with_masks_and_rotation_runs_split_k(variant, geom):
+    """One query row at position p of a longer cache with a causal or window mask, ALiBi measured
+    from p and RoPE: served by the split-K decode kernels (two launches, K/V read once per KV head),
+    not by a 128-row forward tile.  The reference's decode path refuses all of these
+    (attnfuse/runtime/flash_decode.py:46-65)."""
+    Hq, Hkv, D = geom
+    B, L, W, dtype = 2, 3000, 700, torch.bfloat16
+    p = 2345                                            # keys past p exist in the cache and must not be seen
+    Q, K, V = qkv(1700 + Hq, B, Hq, Hkv, 1, L, D, dtype)
+    kw, okw = {}, {"q_offset": p}
+    if "rope" in variant:
+        cos, sin = orc.build_rope_cache(L, D, 500000.0, dtype)
+        kw.update(cos=cos.to(DEV), sin=sin.to(DEV)); okw.update(cos=cos, sin=sin)
+    if "alibi" in variant:
+        okw.update(slopes=_alibi_slopes(Hq, "cpu", str(dtype)), q_positions=torch.full((B,), p))
+    okw["causal"] = "causal" in variant
+    if "window" in variant:
+        okw["window"] = W
+    want = orc.attention(Q, K, V, **okw)
+    from attentionfuse_b200.runtime import _lib
+    before = _lib.launch_count()
+    got = build_graph(variant, Hq, W)(Q.to(DEV), K.to(DEV), V.to(DEV), q_offset=p, **kw)
+    assert _lib.launch_count() - before == 2, "expected the split-K pair of launches"
+    assert_close(got, want, dtype, what=f"single row {variant} {geom}")
+
+
+def test_ragged_batch_decodes_with_rotation_at_each_sequence_end():
+    """Per-sequence lengths and per-sequence query positions (the new token is the last valid key
+    of its sequence): causal + RoPE through the split-K kernels, one oracle call per batch row."""
+    B, Hq, Hkv, L, D, dtype = 4, 16, 4, 2048, 128, torch.float16
+    Q, K, V = qkv(1800, B, Hq, Hkv, 1, L, D, dtype)
+    lens = lens_for(77, B, L)
+    cos, sin = orc.build_rope_cache(L, D, 10000.0, dtype)
+
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+    got = fn(Q.to(DEV), K.to(DEV), V.to(DEV), cos=cos.to(DEV), sin=sin.to(DEV), kv_lens=lens.to(DEV),
+             q_offset=(lens - 1).to(DEV))
+    for b in range(B):
+        n = int(lens[b])
+        want = orc.attention(Q[b:b + 1], K[b:b + 1, :, :n], V[b:b + 1, :, :n], causal=True, cos=cos, sin=sin, q_offset=n - 1)
+        assert_close(got[b:b + 1], want, dtype, what=f"ragged rope row {b}")
+
+
 @pytest.mark.parametrize("splits", [1, 2, 7, 16])
 def test_split_counts_agree(splits):
     B, Hq, Hkv, L, D = 2, 32, 8, 2048, 128
