@@ -42,6 +42,7 @@ int validate_problem(const AfProblem& p) {
   if (p.mask_kind == AF_MASK_BLOCKS) {
     AF_REQUIRE(p.block_m > 0 && p.block_n > 0, "block sizes must be positive");
     AF_REQUIRE(p.kv_num && p.kv_idx, "block lists (kv_num, kv_idx) must be non-NULL");
+    if (p.kv_slot || p.q_slot) AF_REQUIRE(p.kv_bits != nullptr, "bit-matrix numbers (kv_slot / q_slot) need kv_bits");
   }
   if (p.bias_kind == AF_BIAS_ALIBI) AF_REQUIRE(p.slopes != nullptr, "ALiBi needs slopes");
   if (p.bias_kind == AF_BIAS_ADDITIVE) AF_REQUIRE(p.bias != nullptr, "additive bias needs a bias tensor");

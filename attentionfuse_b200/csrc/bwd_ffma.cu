@@ -116,7 +116,10 @@ __global__ void bwd_delta_vec_kernel(const AfBwdParams a) {
 template <typename T, int LD>
 __device__ __forceinline__ void tile_p_ds(const AfBwdParams& a, const float* sQ, const float* sK,
                                           const float* sV, const float* sDO, float* sP, float* sDS,
-                                          int b, int h, int m0, int m_end, int n0, int n_end, float slope) {
+                                          int b, int h, int m0, int m_end, int n0, int n_end, float slope,
+                                          const uint64_t* tile_bits = nullptr, int row_base = 0, int key_base = 0) {
+  // tile_bits: query-major bit matrix of a partially active block whose first row / key are
+  // row_base / key_base; nullptr when every element of the block is active
   const AfProblem& p = a.p;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float s[4][2], dp[4][2];
@@ -164,6 +167,8 @@ __device__ __forceinline__ void tile_p_ds(const AfBwdParams& a, const float* sQ,
                                       (int64_t)row * p.bias_stride[2] + (int64_t)key * p.bias_stride[3]);
       }
       bool keep = (row < m_end) && (key < n_end);
+      if (tile_bits != nullptr && keep)
+        keep = (tile_bits[(int64_t)(row - row_base) * ((p.block_n + 63) / 64) + ((key - key_base) >> 6)] >> ((key - key_base) & 63)) & 1ull;
       if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (row >= key);
       if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(row - key) < p.window);
       // A row with no visible key has L = -inf; its probabilities are zero.
@@ -226,7 +231,7 @@ __global__ void __launch_bounds__(NT) bwd_dkv_ffma_kernel(const AfBwdParams a, c
     const int64_t q_off = (int64_t)b * p.q_stride[0] + (int64_t)h * p.q_stride[1];
     const int64_t g_off = (int64_t)b * a.do_stride[0] + (int64_t)h * a.do_stride[1];
 
-    auto process = [&](const int m0, const int m_end) {
+    auto process = [&](const int m0, const int m_end, const uint64_t* tile_bits, const int row_base) {
       load_tile<T, LD>(sQ, p.q, q_off, p.q_stride[2], p.q_stride[3], m0, m_end, D, DMAX);
       load_tile<T, LD>(sDO, a.d_o, g_off, a.do_stride[2], a.do_stride[3], m0, m_end, D, DMAX);
       __syncthreads();
@@ -234,7 +239,7 @@ __global__ void __launch_bounds__(NT) bwd_dkv_ffma_kernel(const AfBwdParams a, c
         rope_tile<T, LD>(sQ, m0, m_end, D, p.cos, p.sin, p.rope_stride_n);
         __syncthreads();
       }
-      tile_p_ds<T, LD>(a, sQ, sK, sV, sDO, sP, sDS, b, h, m0, m_end, n0, n_end, slope);
+      tile_p_ds<T, LD>(a, sQ, sK, sV, sDO, sP, sDS, b, h, m0, m_end, n0, n_end, slope, tile_bits, row_base, kb * p.block_n);
       __syncthreads();
       for (int m = 0; m < BT; ++m) {
         float pv[4], sv[4], gv[NC], qv[NC];
@@ -262,10 +267,14 @@ __global__ void __launch_bounds__(NT) bwd_dkv_ffma_kernel(const AfBwdParams a, c
     if (p.mask_kind == AF_MASK_BLOCKS) {
       const int n = p.q_num[(int64_t)h * p.q_num_stride_h + kb];
       const int32_t* list = p.q_idx + (int64_t)h * p.q_idx_stride_h + (int64_t)kb * p.q_idx_stride_k;
+      const int32_t* slots = p.q_slot ? p.q_slot + (int64_t)h * p.q_idx_stride_h + (int64_t)kb * p.q_idx_stride_k : nullptr;
+      const int bit_words = (p.block_n + 63) / 64;
       for (int slot = 0; slot < n; ++slot) {
         const int qb = list[slot];
         const int qb_end = min(qb * p.block_m + p.block_m, p.N_q);
-        for (int m0 = qb * p.block_m; m0 < qb_end; m0 += BT) process(m0, min(m0 + BT, qb_end));
+        const int bs = slots ? slots[slot] : -1;
+        const uint64_t* tile_bits = bs >= 0 ? p.kv_bits + (int64_t)bs * p.block_m * bit_words : nullptr;
+        for (int m0 = qb * p.block_m; m0 < qb_end; m0 += BT) process(m0, min(m0 + BT, qb_end), tile_bits, qb * p.block_m);
       }
     } else {
       int lo = 0, hi = p.N_q;
@@ -274,7 +283,7 @@ __global__ void __launch_bounds__(NT) bwd_dkv_ffma_kernel(const AfBwdParams a, c
         lo = max(0, n0 - p.window + 1);
         hi = min(hi, n_end + p.window - 1);
       }
-      for (int m0 = lo; m0 < hi; m0 += BT) process(m0, min(m0 + BT, hi));
+      for (int m0 = lo; m0 < hi; m0 += BT) process(m0, min(m0 + BT, hi), nullptr, 0);
     }
   }
 
@@ -356,7 +365,7 @@ __global__ void __launch_bounds__(NT) bwd_dq_ffma_kernel(const AfBwdParams a, co
 #pragma unroll
     for (int c = 0; c < NC; ++c) dq[i][c] = 0.f;
 
-  auto process = [&](const int n0, const int n_end) {
+  auto process = [&](const int n0, const int n_end, const uint64_t* tile_bits, const int key_base) {
     load_tile<T, LD>(sK, p.k, k_off, p.k_stride[2], p.k_stride[3], n0, n_end, D, DMAX);
     load_tile<T, LD>(sV, p.v, v_off, p.v_stride[2], p.v_stride[3], n0, n_end, D, DMAX);
     __syncthreads();
@@ -364,7 +373,7 @@ __global__ void __launch_bounds__(NT) bwd_dq_ffma_kernel(const AfBwdParams a, co
       rope_tile<T, LD>(sK, n0, n_end, D, p.cos, p.sin, p.rope_stride_n);
       __syncthreads();
     }
-    tile_p_ds<T, LD>(a, sQ, sK, sV, sDO, sP, sDS, b, h, m0, m_end, n0, n_end, slope);
+    tile_p_ds<T, LD>(a, sQ, sK, sV, sDO, sP, sDS, b, h, m0, m_end, n0, n_end, slope, tile_bits, qb * p.block_m, key_base);
     __syncthreads();
     for (int n = 0; n < BT; ++n) {
       float sv[4], kv[NC];
@@ -383,10 +392,14 @@ __global__ void __launch_bounds__(NT) bwd_dq_ffma_kernel(const AfBwdParams a, co
   if (p.mask_kind == AF_MASK_BLOCKS) {
     const int n = p.kv_num[(int64_t)h * p.kv_num_stride_h + qb];
     const int32_t* list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q;
+    const int32_t* slots = p.kv_slot ? p.kv_slot + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q : nullptr;
+    const int bit_words = (p.block_n + 63) / 64;
     for (int slot = 0; slot < n; ++slot) {
       const int kb = list[slot];
       const int kb_end = min(kb * p.block_n + p.block_n, p.N_kv);
-      for (int n0 = kb * p.block_n; n0 < kb_end; n0 += BT) process(n0, min(n0 + BT, kb_end));
+      const int bs = slots ? slots[slot] : -1;
+      const uint64_t* tile_bits = bs >= 0 ? p.kv_bits + (int64_t)bs * p.block_m * bit_words : nullptr;
+      for (int n0 = kb * p.block_n; n0 < kb_end; n0 += BT) process(n0, min(n0 + BT, kb_end), tile_bits, kb * p.block_n);
     }
   } else {
     int lo = 0, hi = p.N_kv;
@@ -395,7 +408,7 @@ __global__ void __launch_bounds__(NT) bwd_dq_ffma_kernel(const AfBwdParams a, co
       lo = max(0, m0 - p.window + 1);
       hi = min(hi, m_end + p.window - 1);
     }
-    for (int n0 = lo; n0 < hi; n0 += BT) process(n0, min(n0 + BT, hi));
+    for (int n0 = lo; n0 < hi; n0 += BT) process(n0, min(n0 + BT, hi), nullptr, 0);
   }
 
   float* sOut = sK;  // reuse

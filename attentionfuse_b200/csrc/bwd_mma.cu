@@ -93,6 +93,8 @@ bool bwd_mma_supports(const AfBwdParams& a, const char** why) {
   if (p.mask_kind == AF_MASK_CAUSAL && p.N_q != p.N_kv) return no("causal with N_q != N_kv");
   if (p.mask_kind == AF_MASK_BLOCKS && (p.block_m % 128 != 0 || p.block_n % 128 != 0))
     return no("block size is not a multiple of 128");
+  if (p.mask_kind == AF_MASK_BLOCKS && (p.kv_slot || p.q_slot) && !(p.kv_slot && p.q_slot && p.kv_bits && p.q_bits))
+    return no("element bit matrices need both list orientations (kv_slot, q_slot, kv_bits, q_bits)");
   if (!tc_tma_ok(p.q, p.B, p.H_q, p.N_q, p.q_stride) || !tc_tma_ok(p.k, p.B, p.H_kv, p.N_kv, p.k_stride) ||
       !tc_tma_ok(p.v, p.B, p.H_kv, p.N_kv, p.v_stride))
     return no("Q/K/V not TMA-addressable");

@@ -51,7 +51,8 @@ using tc::Pack2;
 using tc::ex2_approx;
 
 enum { MODE_DKV = 0, MODE_DQ = 1, MODE_FUSED = 2 };
-enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };   // element-level mask of the instantiation
+enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2, EMASK_BITS = 3 };   // element-level mask of the instantiation
+// (EMASK_BITS: block lists in which some blocks carry a bit matrix of their active elements)
 
 constexpr int BS = 128;   // rows of the stationary operands (TMEM lanes)
 constexpr int BT = 64;    // rows of a streamed tile (columns of S per step)
@@ -105,6 +106,7 @@ struct BwdArgs {
 struct StepWalk {
   int cnt, first;
   const int32_t* list;
+  const int32_t* slots;      // bit-matrix number of each listed block (-1: fully active), or null
   int per, block;
   __device__ __forceinline__ int row0(int s) const {
     if (list != nullptr) return list[s / per] * block + (s % per) * BT;
@@ -115,7 +117,7 @@ struct StepWalk {
 template <int MODE>
 __device__ __forceinline__ StepWalk make_steps(const AfProblem& p, const BwdArgs& args, int tile, int h) {
   StepWalk w;
-  w.list = nullptr; w.per = 1; w.block = BT; w.first = 0;
+  w.list = nullptr; w.slots = nullptr; w.per = 1; w.block = BT; w.first = 0;
   const int t0 = tile * BS;
   if (p.mask_kind == AF_MASK_BLOCKS) {
     const int blk = tile / args.stat_per_block;
@@ -123,10 +125,12 @@ __device__ __forceinline__ StepWalk make_steps(const AfProblem& p, const BwdArgs
     if (MODE != MODE_DQ) {
       w.block = p.block_m;
       w.list = p.q_idx + (int64_t)h * p.q_idx_stride_h + (int64_t)blk * p.q_idx_stride_k;
+      if (p.q_slot != nullptr) w.slots = p.q_slot + (int64_t)h * p.q_idx_stride_h + (int64_t)blk * p.q_idx_stride_k;
       w.cnt = p.q_num[(int64_t)h * p.q_num_stride_h + blk] * w.per;
     } else {
       w.block = p.block_n;
       w.list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)blk * p.kv_idx_stride_q;
+      if (p.kv_slot != nullptr) w.slots = p.kv_slot + (int64_t)h * p.kv_idx_stride_h + (int64_t)blk * p.kv_idx_stride_q;
       w.cnt = p.kv_num[(int64_t)h * p.kv_num_stride_h + blk] * w.per;
     }
   } else if (p.mask_kind == AF_MASK_WINDOW) {
@@ -548,6 +552,17 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         if (EMASK == EMASK_WINDOW)
           need_mask = need_mask || (r0 + BT - 1 - t0 >= p.window) || (t0 + BS - 1 - r0 >= p.window);
         const int rel = srow - r0;   // key-stationary: query c kept iff c >= rel;  DQ: key c kept iff c <= rel
+        uint64_t tile_bits = ~0ull;  // EMASK_BITS: this lane's 64 columns of the block's bit matrix
+        if (EMASK == EMASK_BITS && w.slots != nullptr) {
+          const int bs = w.slots[s / w.per];
+          if (bs >= 0) {
+            // key-stationary: rows of q_bits are keys, bits are queries; DQ: rows of kv_bits are queries
+            const int stat_block = KVS ? p.block_n : p.block_m;
+            const uint64_t* bits = KVS ? p.q_bits : p.kv_bits;
+            tile_bits = bits[((int64_t)bs * stat_block + (t0 % stat_block) + tid) * (w.block >> 6) + (s % w.per)];
+            need_mask = true;
+          }
+        }
 
         uint32_t pk[BT / 2], dk[BT / 2];
         const float relf = (float)rel;
@@ -578,6 +593,7 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
                 bool keep = cc < col_limit;
                 if (EMASK == EMASK_CAUSAL) keep = keep && (KVS ? (cc >= rel) : (cc <= rel));
                 if (EMASK == EMASK_WINDOW) keep = keep && (cc - rel < p.window) && (rel - cc < p.window);
+                if (EMASK == EMASK_BITS) keep = keep && ((tile_bits >> cc) & 1ull);
                 pr = keep ? pr : 0.f;
               }
               pe[u] = pr;
@@ -762,6 +778,12 @@ int launch_composition(const BwdArgs& args, const CUtensorMap& a1, const CUtenso
   const AfProblem& p = args.a.p;
   const int key = (p.mask_kind == AF_MASK_CAUSAL ? 4 : p.mask_kind == AF_MASK_WINDOW ? 8 : 0) +
                   (p.bias_kind == AF_BIAS_ALIBI ? 2 : 0) + (p.rope ? 1 : 0);
+  if (p.mask_kind == AF_MASK_BLOCKS && p.kv_slot != nullptr && p.q_slot != nullptr) {
+    // block lists with element bit matrices (never with rotation: the block-sparse call has none)
+    if (p.rope) return fail(AF_ERR_UNSUPPORTED, "block lists with element bit matrices take no rotation");
+    return p.bias_kind == AF_BIAS_ALIBI ? launch_instance<T, D, MODE, EMASK_BITS, true, false>(args, a1, a2, b1, b2, st)
+                                        : launch_instance<T, D, MODE, EMASK_BITS, false, false>(args, a1, a2, b1, b2, st);
+  }
   switch (key) {
     case 8: return launch_instance<T, D, MODE, EMASK_WINDOW, false, false>(args, a1, a2, b1, b2, st);
     case 9: return launch_instance<T, D, MODE, EMASK_WINDOW, false, true>(args, a1, a2, b1, b2, st);

@@ -99,7 +99,10 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
     for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
   }
 
-  auto process = [&](const int k0, const int k_end) {
+  // tile_bits: bit matrix of a partially active tile whose first key is key_base (rows = queries
+  // from the block's first row), or nullptr when every element of the tile is active
+  const int bit_words = (p.block_n + 63) / 64;
+  auto process = [&](const int k0, const int k_end, const uint64_t* tile_bits, const int key_base) {
     for (int idx = tid; idx < TN * DMAX; idx += NT) {
       const int r = idx / DMAX, d = idx - r * DMAX;
       float kx = 0.f, vx = 0.f;
@@ -150,6 +153,8 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
                                         (int64_t)row * p.bias_stride[2] + (int64_t)key * p.bias_stride[3]);
         }
         bool keep = key < k_end;
+        if (tile_bits != nullptr && keep && row < r_end)
+          keep = (tile_bits[(int64_t)(row - qb * p.block_m) * bit_words + ((key - key_base) >> 6)] >> ((key - key_base) & 63)) & 1ull;
         if (p.mask_kind == AF_MASK_CAUSAL) keep = keep && (pos >= key);
         if (p.mask_kind == AF_MASK_WINDOW) keep = keep && (abs(pos - key) < p.window);
         x = keep ? x : -INFINITY;
@@ -209,10 +214,13 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
   if (p.mask_kind == AF_MASK_BLOCKS) {
     const int n = p.kv_num[(int64_t)h * p.kv_num_stride_h + qb];
     const int32_t* list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q;
+    const int32_t* slots = p.kv_slot ? p.kv_slot + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q : nullptr;
     for (int slot = 0; slot < n; ++slot) {
       const int kb = list[slot];
       const int kb_end = min(kb * p.block_n + p.block_n, p.N_kv);
-      for (int k0 = kb * p.block_n; k0 < kb_end; k0 += TN) process(k0, min(k0 + TN, kb_end));
+      const int bs = slots ? slots[slot] : -1;
+      const uint64_t* tile_bits = bs >= 0 ? p.kv_bits + (int64_t)bs * p.block_m * bit_words : nullptr;
+      for (int k0 = kb * p.block_n; k0 < kb_end; k0 += TN) process(k0, min(k0 + TN, kb_end), tile_bits, kb * p.block_n);
     }
   } else {
     int lo = 0, hi = p.N_kv;
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(NT) fwd_ffma_kernel(const AfFwdParams a, const
       lo = max(0, r0 + p.q_offset - p.window + 1);
       hi = min(hi, r_end + p.q_offset + p.window - 1);
     }
-    for (int k0 = lo; k0 < hi; k0 += TN) process(k0, min(k0 + TN, hi));
+    for (int k0 = lo; k0 < hi; k0 += TN) process(k0, min(k0 + TN, hi), nullptr, 0);
   }
 
   const int64_t o_off = (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1];

@@ -45,7 +45,8 @@ namespace tc {
 using namespace ptx;
 
 enum { ROPE_NONE = 0, ROPE_FUSED = 1 };   // a pre-pass rotation runs the ROPE_NONE kernels
-enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2 };  // element-level mask of the instantiation
+enum { EMASK_NONE = 0, EMASK_CAUSAL = 1, EMASK_WINDOW = 2, EMASK_BITS = 3 };  // element-level mask of the instantiation
+// (EMASK_BITS: block lists in which some tiles carry a bit matrix of their active elements)
 
 constexpr int BM = 128;
 constexpr int BN = 128;
@@ -110,6 +111,7 @@ struct TileWalk {
   int first_tile;            // dense / causal / window: lowest tile index
   int step;                  // +1, or -1 when the tiles are walked from the diagonal down
   const int32_t* list;       // block lists: active key blocks of this query block
+  const int32_t* slots;      // block lists: bit-matrix number of each listed block (-1: fully active), or null
   int per_block;
   __device__ __forceinline__ int key0(int j) const {
     if (list != nullptr) return (list[j / per_block] * per_block + (j % per_block)) * BN;
@@ -120,6 +122,7 @@ struct TileWalk {
 __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& args, int m_blk, int h) {
   TileWalk w;
   w.list = nullptr;
+  w.slots = nullptr;
   w.per_block = 1;
   w.first_tile = 0;
   // Causal + ALiBi: the bias grows towards the diagonal by slope * 128 per tile, so walking up
@@ -132,6 +135,7 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
     const int qb = m_blk / args.q_tiles_per_block;
     w.per_block = args.kv_tiles_per_block;
     w.list = p.kv_idx + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q;
+    if (p.kv_slot != nullptr) w.slots = p.kv_slot + (int64_t)h * p.kv_idx_stride_h + (int64_t)qb * p.kv_idx_stride_q;
     w.n_tiles = p.kv_num[(int64_t)h * p.kv_num_stride_h + qb] * w.per_block;
   } else if (p.mask_kind == AF_MASK_CAUSAL) {
     w.n_tiles = (min(m_end, p.N_kv) + BN - 1) / BN;
@@ -178,7 +182,7 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
     it.split = w / bh_count;
     it.m0 = 0;
     TileWalk& wk = it.walk;
-    wk.list = nullptr; wk.per_block = 1; wk.step = 1;
+    wk.list = nullptr; wk.slots = nullptr; wk.per_block = 1; wk.step = 1;
     it.n_kv = args.kv_lens ? min(max(args.kv_lens[it.b], 0), p.N_kv) : p.N_kv;
     const int tiles = (it.n_kv + BN - 1) / BN;
     wk.first_tile = (int)((int64_t)it.split * tiles / args.num_splits);
@@ -573,6 +577,15 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           need_mask = need_mask || (pos0 + BM - 1 - key0 >= p.window) || (key0 + BN - 1 - pos0 >= p.window);
         const int col0 = key0 + half * HALF_COLS;   // key index of this thread's column 0
         const int rel = row + p.q_offset - col0;    // column c is kept iff ...
+        uint64_t tile_bits = ~0ull;                 // EMASK_BITS: this thread's 64 columns of the tile's bit matrix
+        if (EMASK == EMASK_BITS && walk.slots != nullptr) {
+          const int bs = walk.slots[j / walk.per_block];
+          if (bs >= 0) {
+            const int words = p.block_n >> 6;
+            tile_bits = p.kv_bits[((int64_t)bs * p.block_m + (m0 % p.block_m) + rtid) * words + (j % walk.per_block) * 2 + half];
+            need_mask = true;
+          }
+        }
         if (need_mask) {
           const int kmax = n_kv - col0;             // ... c < kmax
 #pragma unroll
@@ -580,6 +593,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
             bool keep = c < kmax;
             if (EMASK == EMASK_CAUSAL) keep = keep && (c <= rel);
             if (EMASK == EMASK_WINDOW) keep = keep && (c - rel < p.window) && (rel - c < p.window);
+            if (EMASK == EMASK_BITS) keep = keep && ((tile_bits >> c) & 1ull);
             xr[c] = keep ? xr[c] : 0xff800000u;     // -inf
           }
         }
@@ -807,8 +821,18 @@ int launch_composition(const TcArgs& args, const CUtensorMap& mq, const CUtensor
     if constexpr (ROPE == ROPE_NONE) return launch_instance<T, D, ROPE_NONE, EMASK_NONE, false, true>(args, mq, mk, mv, st);
     else return fail(AF_ERR_UNSUPPORTED, "split-K decode takes no rotation");
   }
-  const int em = p.mask_kind == AF_MASK_CAUSAL ? EMASK_CAUSAL : p.mask_kind == AF_MASK_WINDOW ? EMASK_WINDOW : EMASK_NONE;
+  int em = p.mask_kind == AF_MASK_CAUSAL ? EMASK_CAUSAL : p.mask_kind == AF_MASK_WINDOW ? EMASK_WINDOW : EMASK_NONE;
+  if (p.mask_kind == AF_MASK_BLOCKS && p.kv_slot != nullptr) em = EMASK_BITS;
   const bool alibi = p.bias_kind == AF_BIAS_ALIBI;
+  if (em == EMASK_BITS) {
+    // block lists never come with rotation (the block-sparse call has no cos / sin)
+    if constexpr (ROPE == ROPE_NONE) {
+      return alibi ? launch_instance<T, D, ROPE_NONE, EMASK_BITS, true>(args, mq, mk, mv, st)
+                   : launch_instance<T, D, ROPE_NONE, EMASK_BITS, false>(args, mq, mk, mv, st);
+    } else {
+      return fail(AF_ERR_UNSUPPORTED, "block lists with element bit matrices take no rotation");
+    }
+  }
   switch (em * 2 + (alibi ? 1 : 0)) {
     case 0: return launch_instance<T, D, ROPE, EMASK_NONE, false>(args, mq, mk, mv, st);
     case 1: return launch_instance<T, D, ROPE, EMASK_NONE, true>(args, mq, mk, mv, st);

@@ -47,6 +47,7 @@ class AfProblem(C.Structure):
         ("q_num_stride_h", I64), ("q_idx_stride_h", I64), ("q_idx_stride_k", I64),
         ("status", PTR),
         ("q_offset", I32),
+        ("kv_slot", PTR), ("q_slot", PTR), ("kv_bits", PTR), ("q_bits", PTR),
     ]
 
 

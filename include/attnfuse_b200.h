@@ -86,6 +86,17 @@ typedef struct AfProblem {
                          Forward only; no counterpart in the reference, whose kernels index
                          rows and columns from 0 (attnfuse/compiler/codegen.py:126-135,216-217)
                          and reject masks when N_q != N_kv (attnfuse/runtime/dispatch.py:140-148) */
+  /* Element-exact partial tiles (optional; NULL: every listed tile is fully active, which is all
+   * the reference can express because its builder rounds partial tiles up,
+   * attnfuse/runtime/block_mask.py:143-154).  kv_slot is parallel to kv_idx (same strides) and
+   * q_slot to q_idx: -1 = every element of the listed tile is active, s >= 0 = the tile's
+   * elements are given by bit matrix s.  Both orientations of matrix s are stored:
+   *   kv_bits[s][r][w] : row r = query within the tile, bit (c & 63) of word w = c >> 6 = key c,
+   *                      words per row = ceil(block_n / 64)
+   *   q_bits[s][c][w]  : row c = key within the tile, bit (r & 63) of word r >> 6 = query r,
+   *                      words per row = ceil(block_m / 64)   (tensor-core backward only) */
+  const int32_t* kv_slot; const int32_t* q_slot;
+  const uint64_t* kv_bits; const uint64_t* q_bits;
 } AfProblem;
 
 typedef struct AfFwdParams {

@@ -34,6 +34,44 @@ def test_block_mask_builder_matches_reference_lists():
             assert torch.equal(mine[:, : ref.shape[1]], ref)
 
 
+def test_exact_masks_and_the_kernels_tile_view_reproduce_the_elements():
+    """The lists a launch sees (128 x 128 tiles, a bit matrix for every partly covered tile, both
+    orientations) decode back to exactly the element mask they were built from: an exact band mask
+    at block 64 and a block-level mask at block 64 that is re-tiled into quadrant patterns."""
+    from attentionfuse_b200.runtime.block_mask import BlockMask
+
+    def decode(kl, n_q, n_k):
+        def unpack(words):                       # (rows, W) int64 -> (rows, 64 W) bool
+            return ((words.unsqueeze(-1) >> torch.arange(64)) & 1).bool().flatten(-2)
+        T = kl.block_m
+        by_q = torch.zeros(kl.kv_num.shape[0] * T, kl.q_num.shape[0] * T, dtype=torch.bool)
+        by_k = torch.zeros_like(by_q)
+        for qb in range(kl.kv_num.shape[0]):
+            for e in range(int(kl.kv_num[qb])):
+                kb = int(kl.kv_idx[qb, e]); s = -1 if kl.kv_slot is None else int(kl.kv_slot[qb, e])
+                by_q[qb * T:(qb + 1) * T, kb * T:(kb + 1) * T] = True if s < 0 else unpack(kl.kv_bits[s])[:, :T]
+        for kb in range(kl.q_num.shape[0]):
+            for e in range(int(kl.q_num[kb])):
+                qb = int(kl.q_idx[kb, e]); s = -1 if kl.q_slot is None else int(kl.q_slot[kb, e])
+                by_k[qb * T:(qb + 1) * T, kb * T:(kb + 1) * T] = True if s < 0 else unpack(kl.q_bits[s])[:, :T].T
+        return by_q[:n_q, :n_k], by_k[:n_q, :n_k]
+
+    N = 200
+    fn = lambda q, k: (q - k).abs() <= 70
+    qi = torch.arange(N)[:, None].expand(N, N); kj = torch.arange(N)[None, :].expand(N, N)
+    bm = af.create_block_mask(fn, N, N, 64, 64, device="cpu", exact=True)
+    assert bm.n_full < bm.n_active
+    assert bm.kv_num_blocks.sum() + bm.full_kv_num.sum() == bm.n_active
+    a, b = decode(bm.kernel_lists, N, N)
+    assert torch.equal(a, fn(qi, kj)) and torch.equal(b, fn(qi, kj))
+    grid = torch.rand(7, 5, generator=torch.Generator().manual_seed(3)) > 0.5
+    bm = BlockMask.from_dense(grid, 64, 64, device="cpu")
+    want = orc.block_elem_mask(grid, 64, 64, 7 * 64, 5 * 64)
+    a, b = decode(bm.kernel_lists, 7 * 64, 5 * 64)
+    assert bm.kernel_lists.block_m == 128 and torch.equal(a, want) and torch.equal(b, want)
+    assert torch.equal(bm.dense_grid(), grid)
+
+
 def test_block_mask_per_head_roundtrip_and_bigbird_counts():
     rng = np.random.default_rng(0)
     grids = torch.from_numpy(rng.random((3, 7, 5)) < 0.4)
