@@ -145,6 +145,22 @@ class BlockMask:
                          n_active=self.n_active, n_full=self.n_full,
                          kernel_lists=None if self.kernel_lists is None else self.kernel_lists.to(device))
 
+    def slice_heads(self, lo: int, hi: int) -> "BlockMask":
+        """The masks of heads [lo, hi) of a per-head mask (a shared mask is returned as it is): what
+        a rank that owns those heads needs.  Bit-matrix numbers stay global; the matrices are shared."""
+        if not self.per_head:
+            return self
+        cut = lambda t: t[lo:hi]
+        kl = self.kernel_lists
+        if kl is not None:
+            opt = lambda t: None if t is None else t[lo:hi]
+            kl = _KernelLists(kl.block_m, kl.block_n, cut(kl.kv_num), cut(kl.kv_idx), cut(kl.q_num), cut(kl.q_idx),
+                              opt(kl.kv_slot), opt(kl.q_slot), kl.kv_bits, kl.q_bits)
+        return BlockMask(cut(self.kv_num_blocks), cut(self.kv_indices), cut(self.full_kv_num), cut(self.full_kv_idx),
+                         cut(self.q_num_blocks), cut(self.q_indices), self.BLOCK_M, self.BLOCK_N, self.n_q_blocks,
+                         self.n_kv_blocks, int(cut(self.full_kv_num).sum() + cut(self.kv_num_blocks).sum()),
+                         int(cut(self.full_kv_num).sum()), kl)
+
     def fill(self, p: "_lib.AfProblem", H_q: int, backward: bool = False) -> None:
         """Point a parameter block at the lists (query-major always, key-major for backward)."""
         if self.per_head and self.full_kv_num.shape[0] != H_q:

@@ -8,13 +8,17 @@ pass over that batch.  `value` is whole-job TFLOP/s with inputs resident in HBM 
 matmul FLOPs 4*B*H_q*D*N(N+1)/2 per step; under torchrun every rank runs its own batch, weak
 scaling, no collective).  `e2e` is the same metric through the public DSL call with pinned
 host buffers: host->device copies of Q/K/V and the device->host copy of O are inside the timed
-region.  `roofline` compares the forward kernel with the measured bf16 GEMM peak,
-`cpu_baseline` times the CPU oracle on a bounded sample of the same workload, and `extra`
-carries fwd+bwd TFLOP/s and decode GB/s (32k cache, per-sequence lengths) measured in the same
-run, including the KV-sharded decode when N > 1.
+region, next to the plain pinned-copy time of the same bytes (`copy_floor_ms`).  `roofline`
+compares the whole step (rotation pre-pass + attention kernel) with the measured bf16 GEMM peak,
+`cpu_baseline` times the reference's eager CPU path on a bounded sample of the same workload, and
+`extra` carries fwd+bwd TFLOP/s, a sustained (>= 2 s) run of the headline step, decode GB/s (32k
+cache, per-sequence lengths) and, under torchrun, the KV-sharded decode and a strong-scaling leg:
+one problem of each prefill configuration dealt out over the ranks by batch x kv-head.
 
-`--impl reference` times the reference algorithm on the host cores only (the CPU oracle port:
-the reference project is pure Python/Triton and has no compiled CPU path).
+`--impl reference` times the reference algorithm on the host cores only: the reference project's
+own eager functions (attnfuse.reference.naive_attention + rope_utils.apply_rope) loaded from the
+unmodified install under baseline/_ref when it is there, otherwise the CPU oracle port.  The
+reference project is pure Python/Triton and has no compiled CPU path.
 """
 from __future__ import annotations
 
@@ -36,10 +40,10 @@ sys.path.insert(0, str(ROOT))
 CFG4 = dict(B=4, H_q=32, H_kv=8, N=4096, D=128, rope_base=500000.0)
 DECODE = dict(B=16, H_q=32, H_kv=8, L=32768, D=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload,
-# from the ncu capture summarised under profiles/: the capture ran the same shape at batch 2
-# (traffic grows in proportion to the batch) and is scaled to the batch-4 launch here.
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = 264.4e6   # 132.2 MB captured at batch 2 (profiles/fwd_tcgen05_causal_rope_bf16_d128.md), x2 for batch 4
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload:
+# not measured by this run but scaled from an ncu capture of the same shape at batch 2 (132.2 MB;
+# traffic grows in proportion to the batch), and labelled so in the JSON line.
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = 264.4e6
 
 
 def peaks():
@@ -160,22 +164,60 @@ def make_cfg4(device, seed=4000):
     return Q, K, V, dO, cos, sin
 
 
+def load_reference_cpu():
+    """The reference project's own eager CPU functions, from the unmodified install under
+    baseline/_ref, imported under an alias so that they do not collide with this repository's
+    `attnfuse` import path.  Returns (naive_attention, apply_rope) or None when no install is there."""
+    ref = ROOT / "baseline" / "_ref" / "attnfuse"
+    if not (ref / "__init__.py").exists():
+        return None
+    try:
+        import importlib.util
+        if "attnfuse_ref" not in sys.modules:
+            spec = importlib.util.spec_from_file_location("attnfuse_ref", ref / "__init__.py",
+                                                          submodule_search_locations=[str(ref)])
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules["attnfuse_ref"] = mod
+            spec.loader.exec_module(mod)
+        import attnfuse_ref.reference.pytorch_naive as naive
+        import attnfuse_ref.rope_utils as rope
+        return naive.naive_attention, rope.apply_rope
+    except Exception:
+        sys.modules.pop("attnfuse_ref", None)
+        return None
+
+
 def cpu_sample(Q, K, V, cos, sin, threads: int, budget_s: float = 0.0):
-    """Time the CPU oracle on (batch, kv head) groups of the workload (4 query heads x 4096 x 4096
-    each).  One group is always timed; with `budget_s` > 0 as many further groups as fit in that
-    many seconds (at most all 32) are run and the sample's throughput is returned.
-    Returns (TFLOP/s, seconds, groups)."""
+    """Time the reference's CPU path on (batch, kv head) groups of the workload (4 query heads x
+    4096 x 4096 each), fp32 on the rounded bf16 inputs: the reference's own functions composed as
+    its tests compose them (rotate Q and K with apply_rope, expand K/V to the query heads,
+    naive_attention(causal=True)) when the install is there, the oracle port otherwise.  One group
+    is always timed; with `budget_s` > 0 as many further groups as fit in that many seconds (at
+    most all 32) are run and the sample's throughput is returned.
+    Returns (TFLOP/s, seconds, groups, kind)."""
     from oracle import attention_oracle as orc
     torch.set_num_threads(threads)
     g = CFG4["H_q"] // CFG4["H_kv"]
     c, s = cos.float(), sin.float()
-    orc.attention(Q[:1, :1, :512].float(), K[:1, :1, :512].float(), V[:1, :1, :512].float(), causal=True, cos=c, sin=s)
+    ref = load_reference_cpu()
     flops_group = 4.0 * g * CFG4["D"] * causal_pairs(CFG4["N"])
+
+    if ref is not None:
+        naive_attention, apply_rope = ref
+
+        def attend(q, k, v):
+            n = q.shape[2]
+            qr = apply_rope(q.float(), c[:n], s[:n])
+            kr = apply_rope(k.float(), c[:n], s[:n])
+            return naive_attention(qr, kr.expand(-1, q.shape[1], -1, -1), v.float().expand(-1, q.shape[1], -1, -1), causal=True)
+    else:
+        def attend(q, k, v):
+            return orc.attention(q, k, v, causal=True, cos=cos, sin=sin)
+    attend(Q[:1, :1, :512], K[:1, :1, :512], V[:1, :1, :512])
 
     def run_group(i):
         b, kv = divmod(i, CFG4["H_kv"])
-        orc.attention(Q[b:b + 1, kv * g:(kv + 1) * g], K[b:b + 1, kv:kv + 1], V[b:b + 1, kv:kv + 1], causal=True,
-                      cos=cos, sin=sin)
+        attend(Q[b:b + 1, kv * g:(kv + 1) * g], K[b:b + 1, kv:kv + 1], V[b:b + 1, kv:kv + 1])
     t0 = time.perf_counter()
     run_group(0)
     first = time.perf_counter() - t0
@@ -185,11 +227,11 @@ def cpu_sample(Q, K, V, cos, sin, threads: int, budget_s: float = 0.0):
     for i in range(n):
         run_group(i)
     sec = time.perf_counter() - t0
-    return n * flops_group / sec / 1e12, sec, n
+    return n * flops_group / sec / 1e12, sec, n, ("reference" if ref is not None else "port")
 
 
 def run_reference(args):
-    """`--impl reference`: the reference algorithm (CPU oracle port) on the host cores."""
+    """`--impl reference`: the reference's CPU path on the host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -197,7 +239,7 @@ def run_reference(args):
     Q, K, V, dO, cos, sin = make_cfg4("cpu")
     times = []
     for i in range(args.warmup + args.steps):
-        tf, sec, _ = cpu_sample(Q, K, V, cos, sin, threads)
+        tf, sec, _, kind = cpu_sample(Q, K, V, cos, sin, threads)
         if i >= args.warmup:
             times.append(sec)
         if sum(times) > 120:
@@ -206,14 +248,15 @@ def run_reference(args):
     flops = 4.0 * g * CFG4["D"] * causal_pairs(CFG4["N"])
     ms = 1e3 * sum(times) / len(times)
     value = flops / (ms * 1e-3) / 1e12
-    sample = f"1 of {CFG4['B'] * CFG4['H_kv']} (batch, kv-head) groups per step: {g} query heads x 4096 x 4096, fp32 eager"
+    sample = (f"1 of {CFG4['B'] * CFG4['H_kv']} (batch, kv-head) groups per step: {g} query heads x 4096 x 4096, fp32 eager; "
+              "one host process whatever --gpus says, so only the N=1 ratio against it is meaningful")
     print(json.dumps({
         "impl": "reference", "metric": "causal_rope_fwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "llama3-8b attention layer, causal+RoPE forward, Q[4,32,4096,128] K/V[4,8,4096,128]",
                    "sample": sample},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -273,6 +316,14 @@ def main():
     dev = torch.device("cuda", local_rank)
     dist_on = world > 1
     if dist_on:
+        # each rank keeps to its own share of the host cores (copy issue and launch threads of
+        # eight ranks otherwise share whatever the launcher left them on)
+        try:
+            cores = sorted(os.sched_getaffinity(0))
+            per = max(1, len(cores) // world)
+            os.sched_setaffinity(0, cores[local_rank * per:(local_rank + 1) * per] or cores)
+        except (AttributeError, OSError):
+            pass
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
     pk, pk_kind = peaks()
@@ -365,6 +416,20 @@ def main():
     h2d = Qp.numel() * 2 + Kp.numel() * 2 + Vp.numel() * 2
     d2h = Oh.numel() * 2
 
+    # The floor under that number: the same bytes as plain pinned copies, one cudaMemcpyAsync per
+    # tensor, up and down on their own streams at the same time, all ranks at once, no kernel.
+    def copy_only():
+        cur = torch.cuda.current_stream(dev)
+        s_in.wait_stream(cur); s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            Qd.copy_(Qp, non_blocking=True); Kd.copy_(Kp, non_blocking=True); Vd.copy_(Vp, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            Oh.copy_(Od, non_blocking=True)
+        cur.wait_stream(s_in); cur.wait_stream(s_out)
+    for _ in range(2):
+        copy_only()
+    copy_floor_ms = time_region(copy_only, e2e_steps, dist_on) / e2e_steps
+
     result = {
         "metric": "causal_rope_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -373,14 +438,20 @@ def main():
                                "RoPE base 5e5; every rank runs its own batch",
                    "l2": "working set 335 MB per step exceeds the 126 MB L2", "partition": f"batch x kv-head, {world} rank(s), no collective"},
         "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "copy_floor_ms": copy_floor_ms, "copy_floor_frac": copy_floor_ms / e2e_ms,
+                "copy_floor": "the same bytes as plain pinned cudaMemcpyAsync up and down at once, all ranks together, no kernel"},
         "gpu_launches": launches,
         "clocks": clk.summary(),
-        "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": kernel_tflops / pk["bf16_tflops"], "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
-                     "peak_kind": f"{pk_kind} cuBLAS bf16 burst", "kernel": "fwd_tcgen05_kernel<bf16,D=128,causal>",
-                     "kernel_ms": kernel_ms, "step_ms_incl_rope_prepass": ms_step,
-                     "frac_of_nominal_2250": kernel_tflops / 2250.0},
+        # the whole causal+RoPE step: rotation pre-pass + attention kernel, the two launches `value` times
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": per_gpu / pk["bf16_tflops"], "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
+                     "traffic_source": "scaled_from_capture (attention kernel, batch-2 ncu capture x 2)",
+                     "peak_kind": f"{pk_kind} cuBLAS bf16 burst",
+                     "kernel": "rope_prepass_kernel<bf16,128> + fwd_tcgen05_kernel<bf16,D=128,causal> (one step = both launches)",
+                     "step_ms": ms_step, "frac_of_nominal_2250": per_gpu / 2250.0,
+                     "attention_kernel_alone": {"ms": kernel_ms, "tflops": kernel_tflops,
+                                                "frac": kernel_tflops / pk["bf16_tflops"]}},
     }
 
     extra = {}
@@ -406,16 +477,36 @@ def main():
             extra["decode"] = bench_decode(dev, rank, world, dist_on, pk)
         except Exception as e:
             extra["decode"] = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            extra["strong_scaling"] = bench_strong_scaling(dev, rank, world, dist_on, pk)
+        except Exception as e:
+            extra["strong_scaling"] = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            # ---- the headline step back to back for >= 2 s, clocks sampled: what the kernel sustains
+            #      once the part settles under its power cap
+            n_sus = max(50, int(2200.0 / ms_step))
+            for _ in range(20):
+                step()
+            with ClockSampler(local_rank) as clk2:
+                sus_ms = time_region(step, n_sus, dist_on) / n_sus
+            c2 = clk2.summary()
+            sus_tf = flops / (sus_ms * 1e-3) / 1e12
+            extra["sustained"] = {"tflops_per_gpu": sus_tf, "ms_per_step": sus_ms, "steps": n_sus, "seconds": sus_ms * n_sus / 1e3,
+                                  "sm_mhz_median": c2["sm_mhz"], "reasons": c2["reasons"],
+                                  "ms_x_mhz": None if not c2["sm_mhz"] else sus_ms * c2["sm_mhz"],
+                                  "frac_of_sustained_gemm_peak": sus_tf / pk.get("bf16_tflops_sustained", pk["bf16_tflops"])}
+        except Exception as e:
+            extra["sustained"] = {"error": f"{type(e).__name__}: {e}"}
     result["extra"] = extra
 
     if rank == 0:
         try:
             threads = os.cpu_count() or 1
-            tf, sec, groups = cpu_sample(Qh, Kh, Vh, cosh, sinh, threads, budget_s=15.0)
+            tf, sec, groups, kind = cpu_sample(Qh, Kh, Vh, cosh, sinh, threads, budget_s=15.0)
             result["cpu_baseline"] = {
-                "value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "value": tf, "unit": "TFLOP/s", "cores": threads, "kind": kind,
                 "sample": f"{groups} of 32 (batch, kv-head) groups of the workload: 4 query heads x 4096 x 4096 "
-                          f"causal+RoPE each, fp32 eager oracle, {sec:.1f} s"}
+                          f"causal+RoPE each, fp32 eager ({'the reference project\'s own functions' if kind == 'reference' else 'oracle port'}), {sec:.1f} s"}
         except Exception as e:
             result["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                                       "sample": f"failed: {e}"}
@@ -423,6 +514,110 @@ def main():
     if dist_on:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_strong_scaling(dev, rank, world, dist_on, pk):
+    """One problem of each prefill configuration, fixed total size, dealt out over the ranks in
+    units of (batch, kv head) by runtime/partition.shard, no collective in the data path: the
+    Llama-3-8B layer forward + backward (32 units), the GPT-2 geometry causal forward at N = 4096
+    (48 units) and the BigBird per-head block masks forward + backward (32 units, the per-head
+    lists sliced by head).  Time = max over ranks; every rank also runs the whole problem once
+    (untimed) and the concatenated slices of all ranks are compared with it."""
+    import numpy as np
+    import torch.distributed as dist
+    import attentionfuse_b200 as af
+    from attentionfuse_b200.runtime import partition
+    from oracle import attention_oracle as orc
+
+    def gen(seed, shape, dt):
+        g = torch.Generator(device=dev).manual_seed(seed)          # same seed, same GPU model: same bits on every rank
+        return torch.randn(*shape, generator=g, device=dev, dtype=dt)
+
+    @af.attention
+    def causal_rope(Q, K, V):
+        return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+    @af.attention
+    def causal(Q, K, V):
+        return af.softmax(af.causal(af.scaled_dot_product(Q, K))) @ V
+
+    @af.attention
+    def blocks(Q, K, V):
+        return af.softmax(af.block_sparse(af.scaled_dot_product(Q, K))) @ V
+
+    out = {}
+
+    def run_case(name, B, Hq, Hkv, N, D, dt, fn, kw_for, backward, flops):
+        Q, K, V = gen(7100, (B, Hq, N, D), dt), gen(7101, (B, Hkv, N, D), dt), gen(7102, (B, Hkv, N, D), dt)
+        dO = gen(7103, (B, Hq, N, D), dt) if backward else None
+        grp = Hq // Hkv
+        rects = partition.shard(B, Hkv, world, rank)
+
+        def compute(rect_list, sink):
+            for (b0, b1, h0, h1) in rect_list:
+                q, k, v = partition.slice_qkv(Q, K, V, (b0, b1, h0, h1))
+                kw = kw_for(h0 * grp, h1 * grp)
+                if backward:
+                    q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
+                    o = fn(q, k, v, **kw)
+                    o.backward(dO[b0:b1, h0 * grp:h1 * grp])
+                    if sink is not None:
+                        sink["o"][b0:b1, h0 * grp:h1 * grp] = o.detach().float()
+                        sink["dq"][b0:b1, h0 * grp:h1 * grp] = q.grad.float()
+                        sink["dk"][b0:b1, h0:h1] = k.grad.float()
+                        sink["dv"][b0:b1, h0:h1] = v.grad.float()
+                else:
+                    o = fn(q, k, v, **kw)
+                    if sink is not None:
+                        sink["o"][b0:b1, h0 * grp:h1 * grp] = o.float()
+
+        def sinks():
+            s = {"o": torch.zeros(B, Hq, N, D, device=dev)}
+            if backward:
+                s.update(dq=torch.zeros(B, Hq, N, D, device=dev), dk=torch.zeros(B, Hkv, N, D, device=dev),
+                         dv=torch.zeros(B, Hkv, N, D, device=dev))
+            return s
+        mine, whole = sinks(), sinks()
+        compute(rects, mine)                                        # this rank's slices
+        compute(partition.shard(B, Hkv, 1, 0), whole)               # the whole problem on this GPU
+        err = 0.0
+        for key in mine:
+            if dist_on:
+                dist.all_reduce(mine[key])                          # slices are disjoint: the sum concatenates them
+            denom = whole[key].norm().item() or 1.0
+            err = max(err, (mine[key] - whole[key]).norm().item() / denom)
+        del mine, whole
+        for _ in range(2):
+            compute(rects, None)
+        n = 5
+        ms = time_region(lambda: compute(rects, None), n, dist_on) / n
+        ms1 = time_region(lambda: compute(partition.shard(B, Hkv, 1, 0), None), n, False) / n
+        out[name] = {"units": B * Hkv, "ranks": world, "ms_per_step": ms, "tflops_aggregate": flops / (ms * 1e-3) / 1e12,
+                     "ms_whole_problem_on_one_gpu": ms1, "speedup_vs_one_gpu": ms1 / ms,
+                     "rel_fro_slices_vs_whole": err, "backward": backward}
+
+    c = CFG4
+    cos, sin = (t.to(dev) for t in orc.build_rope_cache(c["N"], c["D"], c["rope_base"], torch.bfloat16))
+    run_case("cfg4_llama3_layer_fwd_bwd", c["B"], c["H_q"], c["H_kv"], c["N"], c["D"], torch.bfloat16, causal_rope,
+             lambda h0, h1: dict(cos=cos, sin=sin), True, 3.5 * fwd_flops(c))
+    run_case("cfg2_causal_n4096_fwd", 4, 12, 12, 4096, 64, torch.bfloat16, causal, lambda h0, h1: {}, False,
+             4.0 * 4 * 12 * 64 * causal_pairs(4096))
+    B5, H5, N5, D5, blk = 2, 16, 8192, 64, 128
+    nb = N5 // blk
+    grids = np.zeros((H5, nb, nb), dtype=bool)
+    for h in range(H5):
+        rng = np.random.default_rng(5000 + h)
+        gm = grids[h]
+        gm[:, :2] = True; gm[:2, :] = True
+        for i in range(nb):
+            gm[i, max(0, i - 1):min(nb, i + 2)] = True
+            free = np.flatnonzero(~gm[i])
+            gm[i, rng.choice(free, size=min(3, len(free)), replace=False)] = True
+    mask = af.create_block_mask_per_head(torch.from_numpy(grids), blk, blk, device=dev)
+    run_case("cfg5_bigbird_per_head_fwd_bwd", B5, H5, H5, N5, D5, torch.float16, blocks,
+             lambda h0, h1: dict(block_mask=mask.slice_heads(h0, h1)), True,
+             3.5 * 4.0 * B5 * D5 * blk * blk * float(grids.sum()))
+    return out
 
 
 def _median_ms(fn, warmup=5, iters=20):
