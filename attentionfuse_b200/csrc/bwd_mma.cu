@@ -158,9 +158,8 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
     const int64_t units = (int64_t)p.B * p.H_kv;
     AF_REQUIRE((int64_t)f.tiles * units <= 0x7fffffff - 1024, "too many tiles for one launch");
     f.total_items = (int)(f.tiles * units);
-    int dev = 0, sms = 0;
-    AF_CUDA_OK(cudaGetDevice(&dev));
-    AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    if ((rc = tc_sm_count(&sms)) != AF_OK) return rc;
     f.grid_ctas = (sms > 0 && sms < f.total_items) ? sms : f.total_items;
     // Scheduling chunk: as many (batch, kv head) units as keep their dQ accumulator rows (fp32)
     // and their Q / dO rows inside the L2 (measured at B4 H32/8 N4096: 2 units 2.30 ms, 3: 2.25,
@@ -196,9 +195,8 @@ int launch_bwd_mma(const AfBwdParams& a, cudaStream_t st) {
   AF_REQUIRE((int64_t)dq.tiles * p.B * p.H_q <= 0x7fffffff, "too many tiles for one launch");
   // Persistent launches: one CTA per SM walks its share of the stationary tiles, so that the loads
   // and first products of the next tile overlap the epilogue of the previous one.
-  int dev = 0, sms = 0;
-  AF_CUDA_OK(cudaGetDevice(&dev));
-  AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  if ((rc = tc_sm_count(&sms)) != AF_OK) return rc;
   dkv.total_items = dkv.tiles * p.B * p.H_kv;
   dq.total_items = dq.tiles * p.B * p.H_q;
   dkv.grid_ctas = (sms > 0 && sms < dkv.total_items) ? sms : dkv.total_items;

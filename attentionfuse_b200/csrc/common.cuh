@@ -75,6 +75,7 @@ bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_st
 int tc_make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
                 int box_rows);
 bool tc_tma_ok(const void* ptr, int B, int H, int N, const int64_t* st);
+int tc_sm_count(int* sms);
 int tc_launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st);
 
 int launch_bwd_ffma(const AfBwdParams& a, cudaStream_t st);

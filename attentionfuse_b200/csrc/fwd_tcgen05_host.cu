@@ -1,6 +1,8 @@
 // Host side of the tcgen05 forward: support predicate, TMA descriptor encoding, RoPE mode
 // selection (fused in shared memory vs. a one-off K pre-rotation into caller workspace) and
 // dispatch to the per-(head_dim, RoPE mode) instantiation units.
+#include <mutex>
+
 #include "fwd_tcgen05.cuh"
 
 namespace af {
@@ -24,9 +26,52 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x 128 x 1 x 1.
+// Encoded maps are remembered: a serving or training loop launches the same tensors (same base,
+// extents, strides) over and over, and an encode costs more than the rest of the host side of a
+// launch.  Direct-mapped, keyed by everything the encoding depends on; an entry is a plain value
+// (a map does not own or pin the memory it describes), so a stale one is simply never matched.
+struct MapKey {
+  const void* ptr; int64_t s0, s1, s2; int dtype, B, H, N, D, box;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && s0 == o.s0 && s1 == o.s1 && s2 == o.s2 && dtype == o.dtype && B == o.B && H == o.H &&
+           N == o.N && D == o.D && box == o.box;
+  }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int kMapSlots = 256;
+std::mutex g_map_mu;
+MapSlot g_map_cache[kMapSlots];
+
+size_t map_hash(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (uint64_t)k.N * 0xC2B2AE3D27D4EB4Full + (uint64_t)k.box * 0x165667B19E3779F9ull + (uint64_t)k.H + ((uint64_t)k.B << 20);
+  return (size_t)((h >> 24) % kMapSlots);
+}
+
+int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows);
+
+// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x box_rows x 1 x 1.
 int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
              int box_rows = 128) {
+  const MapKey key{ptr, st[0], st[1], st[2], dtype, B, H, N, D, box_rows};
+  const size_t slot = map_hash(key);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    if (g_map_cache[slot].used && g_map_cache[slot].key == key) {
+      *out = g_map_cache[slot].map;
+      return AF_OK;
+    }
+  }
+  const int rc = encode_map(out, dtype, ptr, B, H, N, D, st, box_rows);
+  if (rc != AF_OK) return rc;
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  g_map_cache[slot].key = key;
+  g_map_cache[slot].map = *out;
+  g_map_cache[slot].used = true;
+  return AF_OK;
+}
+
+int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t esz = 2;
@@ -156,6 +201,22 @@ int launch_prepass(const AfProblem& p, void* q_out, void* k_out, cudaStream_t st
 
 }  // namespace
 
+// Multiprocessor count of the current device, looked up once per device.
+int tc_sm_count(int* sms) {
+  static int cached[64] = {};
+  int dev = 0;
+  AF_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || cached[dev] == 0) {
+    int n = 0;
+    AF_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    if (dev >= 0 && dev < 64) cached[dev] = n;
+    *sms = n;
+    return AF_OK;
+  }
+  *sms = cached[dev];
+  return AF_OK;
+}
+
 int tc_make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
                 int box_rows) {
   return make_map(out, dtype, ptr, B, H, N, D, st, box_rows);
@@ -217,9 +278,8 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
     // One CTA fits per SM (shared memory), so the kernel runs persistently: one CTA per SM walks
     // its share of the query tiles with the pipeline kept full across tile boundaries (measured
     // faster than one CTA per query tile at every size, 951 vs 851 TFLOP/s on causal 4x32x4096x128).
-    int dev = 0, sms = 0;
-    AF_CUDA_OK(cudaGetDevice(&dev));
-    AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
     args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
   }
 
@@ -299,9 +359,8 @@ int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st) {
   args.ws_m = a.ws_m; args.ws_l = a.ws_l; args.ws_acc = a.ws_acc;
   AF_REQUIRE((int64_t)a.num_splits * a.B * a.H_kv <= 0x7fffffff, "too many items for one launch");
   args.total_items = a.num_splits * a.B * a.H_kv;
-  int dev = 0, sms = 0;
-  AF_CUDA_OK(cudaGetDevice(&dev));
-  AF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
   args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
   CUtensorMap mq, mk, mv;
   int rc;

@@ -89,19 +89,22 @@ def attention(fn: Callable) -> Callable:
     @functools.wraps(fn)
     def wrapper(Q, K, V, *, bias=None, cos=None, sin=None, block_mask=None,
                 return_graph: bool = False, **kwargs):
-        key = (Q.shape[-1], str(Q.dtype))
-        graph: Optional[Graph] = traced.get(key)
-        if graph is None:
-            graph = traced[key] = trace_attention_fn(fn, Q, K, V)
+        key = (Q.shape[-1], Q.dtype)
+        entry = traced.get(key)
+        if entry is None:
+            graph = trace_attention_fn(fn, Q, K, V)
             if os.environ.get("ATTNFUSE_DEBUG"):
                 from ..ir.printer import format_graph
                 print(f"[AttnFuse] high-level IR (head_dim={key[0]} dtype={key[1]}):")
                 print(format_graph(graph))
+            # what the routing below needs, looked up once per traced graph instead of per call
+            entry = traced[key] = (graph, MaskKind.BLOCK_SPARSE in {m.kind for m in graph.collect_masks()},
+                                   any(b.kind is BiasKind.ALIBI for b in graph.collect_biases()), [None])
+        graph, is_block_sparse, uses_alibi, backward_ok = entry
         if return_graph:
             return graph
 
-        mask_kinds = {m.kind for m in graph.collect_masks()}
-        if MaskKind.BLOCK_SPARSE in mask_kinds:
+        if is_block_sparse:
             if block_mask is None:
                 raise RuntimeError(
                     "a block-sparse graph needs its block lists at call time: "
@@ -109,7 +112,6 @@ def attention(fn: Callable) -> Callable:
             from ..runtime.block_mask import BlockMask, run_block_sparse
             if not isinstance(block_mask, BlockMask):
                 raise TypeError("block_mask must be an attnfuse.BlockMask")
-            uses_alibi = any(b.kind is BiasKind.ALIBI for b in graph.collect_biases())
             bias_kind = 1 if uses_alibi else 0
             if _wants_grad(Q, K, V):
                 from ..runtime.autograd import AttnFuseBlockSparseFunction
@@ -117,11 +119,13 @@ def attention(fn: Callable) -> Callable:
             return run_block_sparse(Q, K, V, block_mask, 1.0 / (Q.shape[-1] ** 0.5),
                                     bias_kind=bias_kind)
 
-        if _wants_grad(Q, K, V):
-            from ..runtime.backward import can_backward
+        if Q.requires_grad or K.requires_grad or V.requires_grad:
+            if backward_ok[0] is None:
+                from ..runtime.backward import can_backward
+                backward_ok[0] = can_backward(graph)
             # a query position offset (chunked prefill against a cache) is forward only
             off = kwargs.get("q_offset")
-            if can_backward(graph) and (off is None or (isinstance(off, int) and off == 0)):
+            if backward_ok[0] and (off is None or (isinstance(off, int) and off == 0)):
                 from ..runtime.autograd import AttnFuseFunction
                 return AttnFuseFunction.apply(graph, Q, K, V, bias, cos, sin)
             # No backward for this composition: run inference, no gradient flows.

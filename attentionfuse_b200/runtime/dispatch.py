@@ -39,7 +39,24 @@ def _alibi_slopes(n_heads: int, device_str: str, dtype_str: str) -> torch.Tensor
                         device=device_str)
 
 
+_ROPE_VIEWS: dict = {}
+
+
 def _rope_table(t: torch.Tensor, name: str, like: torch.Tensor) -> torch.Tensor:
+    """The (N, D) view of a cos / sin table in Q's dtype on Q's device; the view of a table seen
+    before is remembered (a serving loop passes the same (1, 1, N, D) tables on every call)."""
+    key = (t.data_ptr(), t.shape, t.stride(), t.dtype, like.dtype, like.device)
+    hit = _ROPE_VIEWS.get(key)
+    if hit is not None and hit[0] is t:
+        return hit[1]
+    view = _rope_table_view(t, name, like)
+    if len(_ROPE_VIEWS) >= 16:
+        _ROPE_VIEWS.clear()
+    _ROPE_VIEWS[key] = (t, view)
+    return view
+
+
+def _rope_table_view(t: torch.Tensor, name: str, like: torch.Tensor) -> torch.Tensor:
     if t.dim() == 4:
         t = t.squeeze(0).squeeze(0)
     if t.dim() != 2:
@@ -96,6 +113,24 @@ def validate_qkv(Q, K, V):
         raise ValueError(f"Q/K/V dtypes differ: {Q.dtype}, {K.dtype}, {V.dtype}")
 
 
+# Parameter blocks of the forward launch, filled once per (composition, shapes, strides) and copied
+# per call: a call then sets only the pointers.  The reference pays its launch path on every call
+# (about 40 arguments through the Triton launcher: attnfuse/runtime/dispatch.py:196-214).
+_FWD_TEMPLATES: dict = {}
+_FWD_TEMPLATES_MAX = 256
+# Workspace of forward calls outside autograd (the rotated Q and K of a RoPE problem), kept per
+# (device, stream) and grown on demand: calls on one stream are ordered, so they can share it.
+_INFER_WORKSPACE: dict = {}
+
+
+def _inference_workspace(device, stream: int, need: int) -> torch.Tensor:
+    key = (device.index, stream)
+    ws = _INFER_WORKSPACE.get(key)
+    if ws is None or ws.numel() < need:
+        ws = _INFER_WORKSPACE[key] = torch.empty(need, dtype=torch.uint8, device=device)
+    return ws
+
+
 def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, norm_kind=0,
                    slopes=None, bias=None, cos=None, sin=None, save_lse=None,
                    block_lists=None, family=None, q_offset=0, keep_workspace=None):
@@ -103,24 +138,54 @@ def launch_forward(Q, K, V, out, *, sm_scale, mask_kind, window=0, bias_kind=0, 
     the workspace tensor when the call used one (the rotated Q and K of a RoPE problem, which the
     backward can take over instead of rotating again)."""
     lib = _lib.load()
-    params = _lib.AfFwdParams()
-    keep: list = []
-    fill_problem(params.p, Q, K, V, sm_scale=sm_scale, mask_kind=mask_kind, window=window,
-                 bias_kind=bias_kind, norm_kind=norm_kind, slopes=slopes, bias=bias,
-                 cos=cos, sin=sin, family=family, keep=keep, q_offset=q_offset)
-    if block_lists is not None:
-        block_lists.fill(params.p, Q.shape[1])
-    params.o, params.o_stride = out.data_ptr(), _lib.strides(out)
-    if save_lse is not None:
-        params.lse, params.lse_stride = save_lse.data_ptr(), _lib.strides(save_lse, 3)
-    need = int(lib.af_fwd_workspace_bytes(C.byref(params)))
-    if need > 0 and os.environ.get("ATTNFUSE_ROPE_IN_KERNEL", "0") != "1":
-        workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
-        params.workspace, params.workspace_bytes = workspace.data_ptr(), need
+    if family is None:
+        family = int(os.environ.get("ATTNFUSE_FAMILY", "0"))
+    in_kernel_rope = os.environ.get("ATTNFUSE_ROPE_IN_KERNEL", "0") == "1"
+    key = None
+    if block_lists is None and bias is None:
+        key = (Q.dtype, Q.shape, Q.stride(), K.shape, K.stride(), V.stride(), out.stride(), float(sm_scale), mask_kind,
+               window, bias_kind, norm_kind, family, q_offset, cos is not None and (cos.stride(0), sin.stride(0)),
+               save_lse is not None and save_lse.stride(), (Q.data_ptr() | K.data_ptr() | V.data_ptr() | out.data_ptr()) & 15)
+        hit = _FWD_TEMPLATES.get(key)
+    else:
+        hit = None
+    if hit is not None:
+        template, need = hit
+        params = _lib.AfFwdParams.from_buffer_copy(template)
+        p = params.p
+        p.q, p.k, p.v, params.o = Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr()
+        if slopes is not None:
+            p.slopes = slopes.data_ptr()
+        if cos is not None:
+            p.cos, p.sin = cos.data_ptr(), sin.data_ptr()
+        if save_lse is not None:
+            params.lse = save_lse.data_ptr()
+    else:
+        params = _lib.AfFwdParams()
+        keep: list = []
+        fill_problem(params.p, Q, K, V, sm_scale=sm_scale, mask_kind=mask_kind, window=window,
+                     bias_kind=bias_kind, norm_kind=norm_kind, slopes=slopes, bias=bias,
+                     cos=cos, sin=sin, family=family, keep=keep, q_offset=q_offset)
+        if block_lists is not None:
+            block_lists.fill(params.p, Q.shape[1])
+        params.o, params.o_stride = out.data_ptr(), _lib.strides(out)
+        if save_lse is not None:
+            params.lse, params.lse_stride = save_lse.data_ptr(), _lib.strides(save_lse, 3)
+        need = int(lib.af_fwd_workspace_bytes(C.byref(params)))
+        if key is not None and not keep:
+            if len(_FWD_TEMPLATES) >= _FWD_TEMPLATES_MAX:
+                _FWD_TEMPLATES.clear()
+            _FWD_TEMPLATES[key] = (_lib.AfFwdParams.from_buffer_copy(params), need)
+    stream = _lib.current_stream(Q.device)
+    if need > 0 and not in_kernel_rope:
         if keep_workspace is not None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=Q.device)
             keep_workspace.append(workspace)
+        else:
+            workspace = _inference_workspace(Q.device, stream, need)
+        params.workspace, params.workspace_bytes = workspace.data_ptr(), need
     with _lib.on_device(Q.device):
-        rc = lib.af_fwd(C.byref(params), _lib.current_stream(Q.device))
+        rc = lib.af_fwd(C.byref(params), stream)
     _lib.check(rc, "af_fwd")
     return out
 

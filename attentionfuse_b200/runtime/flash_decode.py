@@ -17,6 +17,7 @@ import torch
 from ..ir.high_level import Graph, BiasKind, MaskKind
 from . import _lib
 
+_DECODE_TEMPLATES: dict = {}
 DECODE_HEAD_DIMS = (64, 128)
 DECODE_DTYPES = (torch.float16, torch.bfloat16)
 
@@ -82,8 +83,8 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     _, H_kv, N_kv, _ = K.shape
     if V.stride() != K.stride() and (V.stride(3) != 1 or any(s % 8 for s in V.stride()[:3])):
         V = V.contiguous()
-    dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     if num_splits is None:
+        dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
         num_splits = _pick_num_splits(B, H_q, H_kv, N_kv, dev_index, kv_lens is not None)
     ws_m, ws_l, ws_acc = workspace if workspace is not None else decode_workspace(
         num_splits, B, H_q, D, Q.device)
@@ -101,23 +102,37 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                                     or not q_positions.is_contiguous()):
         q_positions = q_positions.to(device=Q.device, dtype=torch.int32).contiguous()
 
-    p = _lib.AfDecodeParams()
-    p.dtype = _lib.dtype_code(Q.dtype)
-    p.B, p.H_q, p.H_kv, p.N_kv, p.D = B, H_q, H_kv, N_kv, D
-    p.sm_scale, p.bias_kind, p.num_splits = float(sm_scale), int(bias_kind), int(num_splits)
-    p.q, p.q_stride = Q.data_ptr(), _lib.strides(Q)
-    p.k, p.k_stride = K.data_ptr(), _lib.strides(K)
-    p.v, p.v_stride = V.data_ptr(), _lib.strides(V)
+    # the shape / stride / flag part of the parameter block is filled once per distinct problem and
+    # copied afterwards: a decode step at short caches is bound by this call path
+    key = (Q.dtype, Q.shape, Q.stride(), K.shape, K.stride(), V.stride(), None if out is None else out.stride(),
+           float(sm_scale), int(bias_kind), int(num_splits), int(kv_offset), int(mask_kind), int(window or 0),
+           q_position, cos is not None and cos.stride(0))
+    template = _DECODE_TEMPLATES.get(key)
+    if template is None:
+        p = _lib.AfDecodeParams()
+        p.dtype = _lib.dtype_code(Q.dtype)
+        p.B, p.H_q, p.H_kv, p.N_kv, p.D = B, H_q, H_kv, N_kv, D
+        p.sm_scale, p.bias_kind, p.num_splits = float(sm_scale), int(bias_kind), int(num_splits)
+        p.q_stride, p.k_stride, p.v_stride = _lib.strides(Q), _lib.strides(K), _lib.strides(V)
+        p.kv_offset = int(kv_offset)
+        p.mask_kind, p.window = int(mask_kind), int(window or 0)
+        if q_position is not None:
+            p.q_position_p1 = int(q_position) + 1
+        if cos is not None:
+            p.rope, p.rope_stride_n = 1, cos.stride(0)
+        if out is not None:
+            p.o_stride = _lib.strides(out)
+        if len(_DECODE_TEMPLATES) >= 256:
+            _DECODE_TEMPLATES.clear()
+        template = _DECODE_TEMPLATES[key] = p
+    p = _lib.AfDecodeParams.from_buffer_copy(template)
+    p.q, p.k, p.v = Q.data_ptr(), K.data_ptr(), V.data_ptr()
     p.slopes, p.kv_lens, p.q_positions = _lib.ptr(slopes), _lib.ptr(kv_lens), _lib.ptr(q_positions)
-    p.kv_offset = int(kv_offset)
-    p.mask_kind, p.window = int(mask_kind), int(window or 0)
-    if q_position is not None:
-        p.q_position_p1 = int(q_position) + 1
     if cos is not None:
-        p.rope, p.cos, p.sin, p.rope_stride_n = 1, cos.data_ptr(), sin.data_ptr(), cos.stride(0)
+        p.cos, p.sin = cos.data_ptr(), sin.data_ptr()
     p.ws_m, p.ws_l, p.ws_acc = ws_m.data_ptr(), ws_l.data_ptr(), ws_acc.data_ptr()
     if out is not None:
-        p.o, p.o_stride = out.data_ptr(), _lib.strides(out)
+        p.o = out.data_ptr()
     if partial is not None:
         p.partial = partial.data_ptr()
     with _lib.on_device(Q.device):
