@@ -144,6 +144,11 @@ int af_decode_combine_push(const AfDecodeParams* params, const AfPeerExchange* e
   return launch_decode_combine_push(*params, exchange, static_cast<cudaStream_t>(stream));
 }
 
+int af_decode_sharded_step(const AfDecodeParams* params, const AfPeerExchange* exchange, int32_t mode, af_stream_t stream) {
+  if (params == nullptr) return fail(AF_ERR_INVALID, "params is NULL");
+  return launch_decode_sharded_step(*params, exchange, mode, static_cast<cudaStream_t>(stream));
+}
+
 int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32_t H_q, int32_t D, int32_t dtype, void* o,
                          const int64_t o_stride[4], af_stream_t stream) {
   return launch_decode_wait_merge(exchange, B, H_q, D, dtype, o, o_stride, static_cast<cudaStream_t>(stream));

@@ -94,6 +94,7 @@ int launch_decode_combine(const AfDecodeParams& a, cudaStream_t st);
 int launch_decode_static(const AfDecodeParams& a, cudaStream_t st);
 int64_t decode_exchange_bytes(int world, int B, int H_q, int D);
 int launch_decode_combine_push(const AfDecodeParams& a, const AfPeerExchange* x, cudaStream_t st);
+int launch_decode_sharded_step(const AfDecodeParams& a, const AfPeerExchange* x, int mode, cudaStream_t st);
 int launch_decode_wait_merge(const AfPeerExchange* x, int B, int H_q, int D, int dtype, void* o, const int64_t* os,
                              cudaStream_t st);
 int launch_decode_combine_gathered(const float* gathered, int G, int B, int H_q, int D,

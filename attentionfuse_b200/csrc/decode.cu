@@ -100,8 +100,40 @@ __device__ __forceinline__ void rotate_words(uint32_t& lo, uint32_t& hi, uint32_
 // KPW = keys of each 64-key tile one warp handles (16: warps split keys; 64: warps split heads).
 // ROPE: the query row is rotated in registers at its position, every K tile in place in shared
 // memory at the keys' positions, before the dot.
-template <typename T, int D, int KPW, bool ROPE>
-__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks) {
+// System-scope flag accesses of the fused exchange (plain peer stores carry the data; one
+// system-scope fence orders them before the flag).
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Exchange buffer layout (the same as the two-kernel exchange uses): per parity
+// o[world][rows][D], then lse[2][world][rows], then flag[2][world].
+struct XLayout {
+  int64_t o_floats, lse_floats;
+  __device__ XLayout(int world, int rows, int D) : o_floats((int64_t)world * rows * D), lse_floats((int64_t)world * rows) {}
+  __device__ int64_t o_off(int parity, int src, int rows, int D) const { return parity * o_floats + (int64_t)src * rows * D; }
+  __device__ int64_t lse_off(int parity, int src, int rows) const { return 2 * o_floats + parity * lse_floats + (int64_t)src * rows; }
+  __device__ int64_t flag_off() const { return 2 * o_floats + 2 * lse_floats; }
+};
+
+enum { XMODE_NONE = 0, XMODE_PUSH = 1, XMODE_MERGE = 2, XMODE_STEP = 3 };
+
+// XMODE (fused KV-sharded step, one launch): XMODE_PUSH -- after its partials are written, a CTA
+// takes a ticket of its (batch, kv head[, head chunk]) unit; the unit's last CTA merges the
+// unit's splits and stores the normalised rows and their log-sum-exps into slot `rank` of every
+// rank's exchange buffer (plain peer stores), and the CTA that completes the last unit raises this
+// rank's flag on every rank.  XMODE_MERGE -- that same CTA then waits (bounded) for all ranks'
+// flags and merges its unit's rows from this rank's own buffer into O.  Every CTA of the launch
+// must be resident at once (checked by the host), because the waiting CTAs keep their slots.
+template <typename T, int D, int KPW, bool ROPE, bool FUSED = false>
+__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks,
+                                                                   const AfPeerExchange x = AfPeerExchange{},
+                                                                   const int xmode = XMODE_NONE) {
   constexpr int ROW_BYTES = D * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;       // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_BN * ROW_BYTES;
@@ -117,6 +149,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x;
+  // fused step: the step number this launch produces (push) or consumes (merge only); read before
+  // any CTA can complete the launch's last unit, which is what advances it
+  uint32_t xstep = 0;
+  if (FUSED) xstep = x.state[0] + ((xmode & XMODE_PUSH) ? 1u : 0u);
   int bid = blockIdx.y;
   const int chunk = bid % head_chunks; bid /= head_chunks;
   const int h_kv = bid % a.H_kv;
@@ -160,6 +196,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
     }
   };
 
+  if (!FUSED || (xmode & XMODE_PUSH)) {
   // Query fragments: rows g and g+8 of the M tile; rows past the group are zero.
   uint32_t qf[KSTEPS][4];
   {
@@ -390,6 +427,127 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
             make_float2(o[i][2 * row], o[i][2 * row + 1]);
     }
   }
+  }   // split work
+
+  if (FUSED) {
+    constexpr int VEC = D / 32;
+    __shared__ int s_last, s_failed;
+    const int rows = a.B * a.H_q;
+    const int parity = xstep & 1;
+    const XLayout lay(x.world, rows, D);
+    const int unit = blockIdx.y;
+    const int n_units = gridDim.y;
+    const int unit_rows = min(group - chunk * 64, 64);
+    const int row0 = b * a.H_q + h_kv * group + chunk * 64;          // first (batch, head) row of the unit
+    uint32_t* tickets = x.state + 2;
+    bool last = false;
+    if (xmode & XMODE_PUSH) {
+      __threadfence();                                               // this CTA's partials, device-wide
+      __syncthreads();
+      if (tid == 0) {
+        const uint32_t got = atomicAdd(&tickets[unit], 1u);
+        s_last = (got == (uint32_t)a.num_splits - 1u);
+        if (s_last) tickets[unit] = 0u;                              // ready for the next step
+        s_failed = 0;
+      }
+      __syncthreads();
+      last = s_last != 0;
+      if (last) {
+        __threadfence();                                             // the other CTAs' partials
+        for (int r = warp; r < unit_rows; r += DEC_THREADS / 32) {
+          const int row = row0 + r;
+          float mstar = -INFINITY;
+          for (int s = 0; s < a.num_splits; ++s) mstar = fmaxf(mstar, a.ws_m[(int64_t)s * rows + row]);
+          const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+          float acc[VEC];
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+          float lsum = 0.f;
+          for (int s = 0; s < a.num_splits; ++s) {
+            const int64_t wr = (int64_t)s * rows + row;
+            const float w = expf(a.ws_m[wr] - m_use);
+            lsum += w * a.ws_l[wr];
+            const float* src = a.ws_acc + wr * D + lane * VEC;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] += w * src[i];
+          }
+          const float inv = lsum == 0.f ? 0.f : 1.f / lsum;
+          const float lse = lsum == 0.f ? -INFINITY : mstar + logf(lsum);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] *= inv;
+          for (int peer = 0; peer < x.world; ++peer) {
+            float* base = reinterpret_cast<float*>(x.peer_bases[peer]);
+            float* dst = base + lay.o_off(parity, x.rank, rows, D) + (int64_t)row * D + lane * VEC;
+            if constexpr (VEC == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            else *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+            if (lane == 0) base[lay.lse_off(parity, x.rank, rows) + row] = lse;
+          }
+        }
+        __syncthreads();
+        if (tid == 0) {
+          __threadfence_system();                                    // the unit's peer stores before the count
+          const uint32_t done = atomicAdd(&x.state[1], 1u);
+          if (done == (uint32_t)n_units - 1u) {
+            x.state[1] = 0u;
+            __threadfence_system();
+            for (int peer = 0; peer < x.world; ++peer) {
+              uint32_t* flags = reinterpret_cast<uint32_t*>(reinterpret_cast<float*>(x.peer_bases[peer]) + lay.flag_off());
+              st_relaxed_sys_u32(flags + parity * x.world + x.rank, xstep);
+            }
+            x.state[0] = xstep;
+            __threadfence();
+          }
+        }
+      }
+    } else {
+      last = split == 0;                                             // merge-only launch: one CTA per unit
+      if (tid == 0) s_failed = 0;
+      __syncthreads();
+    }
+    if ((xmode & XMODE_MERGE) && last) {
+      const float* base = reinterpret_cast<const float*>(x.peer_bases[x.rank]);
+      const uint32_t* flags = reinterpret_cast<const uint32_t*>(base + lay.flag_off()) + parity * x.world;
+      if (tid < x.world) {
+        const long long limit = x.wait_cycles > 0 ? x.wait_cycles : (1ll << 31);
+        const long long t0 = clock64();
+        // flags only grow; a flag at or past the step (modulo wrap) means that rank's rows landed
+        while ((int32_t)(ld_acquire_sys_u32(flags + tid) - xstep) < 0) {
+          if (clock64() - t0 > limit) { s_failed = 1; break; }
+        }
+      }
+      __syncthreads();
+      if (s_failed) {
+        if (tid == 0 && x.status != nullptr) atomicExch(x.status, AF_STATUS_WAIT_TIMEOUT);
+      } else {
+        for (int r = warp; r < unit_rows; r += DEC_THREADS / 32) {
+          const int row = row0 + r;
+          float w[32];
+          float mstar = -INFINITY;
+#pragma unroll 8
+          for (int rk = 0; rk < x.world; ++rk) {
+            w[rk & 31] = base[lay.lse_off(parity, rk, rows) + row];
+            mstar = fmaxf(mstar, w[rk & 31]);
+          }
+          const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+          float wsum = 0.f;
+#pragma unroll 8
+          for (int rk = 0; rk < x.world; ++rk) {
+            w[rk & 31] = (w[rk & 31] == -INFINITY) ? 0.f : expf(w[rk & 31] - m_use);
+            wsum += w[rk & 31];
+          }
+          const float inv = (mstar == -INFINITY) ? 0.f : 1.f / wsum;
+          T* dst = reinterpret_cast<T*>(a.o) + (int64_t)(row / a.H_q) * a.o_stride[0] + (int64_t)(row % a.H_q) * a.o_stride[1];
+          for (int dd = lane; dd < D; dd += 32) {
+            float acc = 0.f;
+#pragma unroll 8
+            for (int rk = 0; rk < x.world; ++rk)
+              if (w[rk & 31] != 0.f) acc += w[rk & 31] * base[lay.o_off(parity, rk, rows, D) + (int64_t)row * D + dd];
+            dst[(int64_t)dd * a.o_stride[3]] = Elem<T>::from_f32(acc * inv);
+          }
+        }
+      }
+    }
+  }
 }
 
 // Merge the per-split partials of one (batch, head) row: one warp per row, float4 lanes.
@@ -473,7 +631,7 @@ int launch_split_impl(const AfDecodeParams& a, cudaStream_t st) {
   do {                                                                                                    \
     auto kern = decode_split_kernel<T, D, KPW, ROPE>;                                                     \
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
-    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks);                                                \
+    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks, AfPeerExchange{}, (int)XMODE_NONE);             \
   } while (0)
   if (group <= 16) {
     if (a.rope) AF_DECODE_LAUNCH(16, true); else AF_DECODE_LAUNCH(16, false);
@@ -596,6 +754,63 @@ int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
   if (decode_tc_supports(a)) return launch_decode_split_tc(a, st);
   if (a.dtype == AF_F16) return a.D == 64 ? launch_split_impl<__half, 64>(a, st) : launch_split_impl<__half, 128>(a, st);
   return a.D == 64 ? launch_split_impl<__nv_bfloat16, 64>(a, st) : launch_split_impl<__nv_bfloat16, 128>(a, st);
+}
+
+// The KV-sharded step as ONE launch: split-K over this rank's keys, the per-unit merge with the
+// push to every rank's exchange buffer, and (mode bit 2) the bounded wait for the other ranks with
+// the final merge.  Mode 1 and mode 2 as separate launches run the two halves on their own, which
+// is how several "ranks" are exercised on one GPU (all pushes first, then the merges): kernels
+// that wait for one another must never be separate launches on one device.
+template <typename T, int D>
+int launch_sharded_impl(const AfDecodeParams& a, const AfPeerExchange& x, int mode, cudaStream_t st) {
+  const int group = a.H_q / a.H_kv;
+  const int head_chunks = (group + 63) / 64;
+  const size_t smem = (size_t)2 * DEC_STAGES * DEC_BN * D * 2;
+  dim3 grid(a.num_splits, a.B * a.H_kv * head_chunks);
+#define AF_SHARDED_LAUNCH(KPW, ROPE)                                                                      \
+  do {                                                                                                    \
+    auto kern = decode_split_kernel<T, D, KPW, ROPE, true>;                                               \
+    AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+    if (mode & XMODE_MERGE) {                                                                             \
+      /* waiting CTAs keep their slots: every CTA of the launch has to be resident at once */             \
+      int per_sm = 0, sms = 0;                                                                            \
+      AF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, DEC_THREADS, smem));        \
+      { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }                          \
+      if ((int64_t)grid.x * grid.y > (int64_t)per_sm * sms)                                               \
+        return fail(AF_ERR_INVALID, "fused sharded step: %lld CTAs exceed the %lld that are resident at once; "  \
+                    "lower num_splits", (long long)grid.x * grid.y, (long long)per_sm * sms);             \
+    }                                                                                                     \
+    kern<<<grid, DEC_THREADS, smem, st>>>(a, head_chunks, x, mode);                                       \
+  } while (0)
+  if (group <= 16) {
+    if (a.rope) AF_SHARDED_LAUNCH(16, true); else AF_SHARDED_LAUNCH(16, false);
+  } else {
+    if (a.rope) AF_SHARDED_LAUNCH(64, true); else AF_SHARDED_LAUNCH(64, false);
+  }
+#undef AF_SHARDED_LAUNCH
+  count_launch();
+  return check_cuda(cudaGetLastError(), "decode_sharded_step launch");
+}
+
+int launch_decode_sharded_step(const AfDecodeParams& a, const AfPeerExchange* x, int mode, cudaStream_t st) {
+  int rc = validate_decode(a);
+  if (rc != AF_OK) return rc;
+  AF_REQUIRE(x != nullptr && x->world >= 1 && x->world <= 32 && x->rank >= 0 && x->rank < x->world, "bad exchange");
+  AF_REQUIRE(x->peer_bases != nullptr && x->state != nullptr, "exchange pointers must be non-NULL");
+  AF_REQUIRE(mode >= XMODE_PUSH && mode <= XMODE_STEP, "mode must be 1 (push), 2 (merge) or 3 (whole step)");
+  AF_REQUIRE(a.q && a.k && a.v, "q/k/v must be non-NULL");
+  AF_REQUIRE(!(mode & XMODE_MERGE) || a.o != nullptr, "the merge writes o");
+  AF_REQUIRE(a.q_stride[3] == 1 && a.k_stride[3] == 1 && a.v_stride[3] == 1, "decode needs unit inner strides");
+  AF_REQUIRE(a.k_stride[2] % 8 == 0 && a.v_stride[2] % 8 == 0 && a.k_stride[1] % 8 == 0 && a.v_stride[1] % 8 == 0 &&
+                 a.k_stride[0] % 8 == 0 && a.v_stride[0] % 8 == 0 && ((uintptr_t)a.k % 16) == 0 && ((uintptr_t)a.v % 16) == 0,
+             "decode needs 16-byte aligned K/V rows");
+  AF_REQUIRE(((uintptr_t)a.q % 4) == 0 && a.q_stride[1] % 2 == 0 && a.q_stride[0] % 2 == 0, "decode needs 4-byte aligned Q rows");
+  AF_REQUIRE(a.bias_kind == AF_BIAS_NONE || (a.bias_kind == AF_BIAS_ALIBI && a.slopes), "bad bias_kind for decode");
+  AF_REQUIRE(a.mask_kind == AF_MASK_FULL || a.mask_kind == AF_MASK_CAUSAL || (a.mask_kind == AF_MASK_WINDOW && a.window > 0),
+             "decode takes full, causal or window masks");
+  if (a.rope) AF_REQUIRE(a.cos && a.sin && a.rope_stride_n % 8 == 0, "RoPE decode needs 16-byte aligned cos / sin tables");
+  if (a.dtype == AF_F16) return a.D == 64 ? launch_sharded_impl<__half, 64>(a, *x, mode, st) : launch_sharded_impl<__half, 128>(a, *x, mode, st);
+  return a.D == 64 ? launch_sharded_impl<__nv_bfloat16, 64>(a, *x, mode, st) : launch_sharded_impl<__nv_bfloat16, 128>(a, *x, mode, st);
 }
 
 int launch_decode_combine(const AfDecodeParams& a, cudaStream_t st) {

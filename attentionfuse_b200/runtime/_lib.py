@@ -94,7 +94,7 @@ class AfPeerExchange(C.Structure):
                 ("wait_cycles", I64)]
 
 
-EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_bwd_dq_accum_bytes", "af_decode_split", "af_decode_combine", "af_decode_static", "af_decode_exchange_bytes", "af_decode_combine_push", "af_decode_wait_merge",
+EXPORTS = ("af_fwd", "af_fwd_workspace_bytes", "af_bwd", "af_bwd_workspace_bytes", "af_bwd_dq_accum_bytes", "af_decode_split", "af_decode_combine", "af_decode_static", "af_decode_exchange_bytes", "af_decode_combine_push", "af_decode_wait_merge", "af_decode_sharded_step",
            "af_decode_combine_gathered", "af_decode_num_splits", "af_query_family",
            "af_launch_count", "af_last_error", "af_abi_version")
 
@@ -133,6 +133,8 @@ def load() -> C.CDLL:
         lib.af_decode_combine_push.restype = I32
         lib.af_decode_wait_merge.argtypes = [C.POINTER(AfPeerExchange), I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]
         lib.af_decode_wait_merge.restype = I32
+        lib.af_decode_sharded_step.argtypes = [C.POINTER(AfDecodeParams), C.POINTER(AfPeerExchange), I32, PTR]
+        lib.af_decode_sharded_step.restype = I32
         lib.af_decode_static.argtypes = [C.POINTER(AfDecodeParams), PTR]
         lib.af_decode_static.restype = I32
         lib.af_decode_combine_gathered.argtypes = [PTR, I32, I32, I32, I32, I32, PTR, C.POINTER(I64), PTR]

@@ -73,7 +73,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      alibi_slopes: Optional[torch.Tensor] = None, kv_offset: int = 0,
                      q_positions: Optional[torch.Tensor] = None,
                      partial: Optional[torch.Tensor] = None,
-                     num_splits: Optional[int] = None, workspace=None, exchange=None,
+                     num_splits: Optional[int] = None, workspace=None, exchange=None, exchange_mode: int = 0,
                      mask_kind: int = 0, window: int = 0, q_position: Optional[int] = None,
                      cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
@@ -137,6 +137,11 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         p.partial = partial.data_ptr()
     with _lib.on_device(Q.device):
         stream = _lib.current_stream(Q.device)
+        if exchange is not None and exchange_mode:
+            # KV-sharded step in one launch (3), or its push (1) / merge (2) half
+            _lib.check(lib.af_decode_sharded_step(C.byref(p), C.byref(exchange.c), int(exchange_mode), stream),
+                       "af_decode_sharded_step")
+            return out
         _lib.check(lib.af_decode_split(C.byref(p), stream), "af_decode_split")
         if exchange is not None:
             # KV-sharded step: the combine pushes this rank's partial to every rank's exchange

@@ -122,7 +122,7 @@ class PeerExchange:
     one after another."""
 
     def __init__(self, world: int, rank: int, B: int, H_q: int, D: int, device, *, group=None,
-                 peer_buffers=None, wait_cycles: int = 0):
+                 peer_buffers=None, wait_cycles: int = 0, units: int = 0):
         import ctypes as C
         from . import _lib
         lib = _lib.load()
@@ -144,7 +144,9 @@ class PeerExchange:
             ptrs = [t.data_ptr() for t in peer_buffers]
         self.n_floats = n_floats
         self.peer_bases = torch.tensor(ptrs, dtype=torch.int64, device=device)
-        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        # step counter, unit counter, then one ticket word per (batch, kv head, head chunk) unit
+        # for the single-launch step
+        self.state = torch.zeros(2 + max(int(units), B * H_q), dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.c = _lib.AfPeerExchange(world, rank, self.peer_bases.data_ptr(), self.state.data_ptr(),
                                      self.status.data_ptr(), int(wait_cycles))
@@ -157,6 +159,15 @@ class PeerExchange:
                                           out.data_ptr(), _lib.strides(out), _lib.current_stream(out.device))
         _lib.check(rc, "af_decode_wait_merge")
         return out
+
+    def sharded_step(self, params, mode: int, device) -> None:
+        """One launch of the fused step (mode 3), or its push / merge half (1 / 2)."""
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load()
+        with _lib.on_device(device):
+            rc = lib.af_decode_sharded_step(C.byref(params), C.byref(self.c), int(mode), _lib.current_stream(device))
+        _lib.check(rc, "af_decode_sharded_step")
 
     def check_status(self) -> None:
         """Raise if a bounded wait ran out (synchronises)."""
@@ -175,10 +186,11 @@ class ShardedDecodePlan:
     def __init__(self, B: int, H_q: int, H_kv: int, D: int, L_total: int, rank: int, world: int,
                  kv_lens: Optional[torch.Tensor], device, dtype, *, sm_scale: Optional[float] = None,
                  bias_kind: int = 0, slopes=None, group=None, layout: str = "contiguous",
-                 exchange: str = "nccl"):
+                 exchange: str = "nccl", peer_exchange: Optional["PeerExchange"] = None):
         from .flash_decode import _pick_num_splits, decode_workspace
-        if exchange not in ("nccl", "p2p"):
+        if exchange not in ("nccl", "p2p", "fused"):
             raise ValueError(f"unknown exchange {exchange!r}")
+        self.fused = exchange == "fused"
         self.exchange = None
         self.rank, self.world, self.group = rank, world, group
         self.H_kv, self.bias_kind = H_kv, bias_kind
@@ -202,15 +214,31 @@ class ShardedDecodePlan:
         index = device.index if getattr(device, "index", None) is not None else torch.cuda.current_device()
         self.kv_offset = self.lo if layout == "contiguous" else 0
         self.num_splits = _pick_num_splits(B, H_q, H_kv, max(self.hi - self.lo, 1), index, kv_lens is not None)
+        if self.fused:
+            # one launch for the whole step: every CTA must be resident at once (two per SM), and a
+            # rank's share of a 32k cache is short, so one wave of long CTAs beats several of short ones
+            from .flash_decode import _sm_count
+            units = B * H_kv * ((H_q // H_kv + 63) // 64)
+            self.num_splits = max(1, min((2 * _sm_count(index)) // units, max(1, (self.hi - self.lo) // 256)))
         self.workspace = decode_workspace(self.num_splits, B, H_q, D, device)
         self.partial = torch.empty(B, H_q, D + 1, dtype=torch.float32, device=device)
         self.gathered = torch.empty(world, B, H_q, D + 1, dtype=torch.float32, device=device)
-        if exchange == "p2p" and world > 1:
-            self.exchange = PeerExchange(world, rank, B, H_q, D, device, group=group)
+        if exchange in ("p2p", "fused"):
+            if peer_exchange is not None:       # buffers set up by the caller (single-GPU emulation of the ranks)
+                self.exchange = peer_exchange
+            elif world > 1:
+                self.exchange = PeerExchange(world, rank, B, H_q, D, device, group=group)
 
     def step(self, Q: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
         from .flash_decode import run_flash_decode, combine_gathered
+        if self.exchange is not None and self.fused:
+            # one launch: split-K, per-unit merge + push to all peers, wait for the peers, final merge
+            run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, out,
+                             kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
+                             q_positions=self.q_positions, num_splits=self.num_splits,
+                             workspace=self.workspace, exchange=self.exchange, exchange_mode=3)
+            return out
         if self.exchange is not None:
             # two launches of the local decode (split, combine + push to all peers) and the
             # wait + merge kernel; no library collective

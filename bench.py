@@ -894,6 +894,39 @@ def bench_decode(dev, rank, world, dist_on, pk):
                                           res.get("graph_ms_per_step", ms) / msg3})
         except Exception as e:
             res["kv_sharded_p2p_error"] = f"{type(e).__name__}: {e}"
+        try:   # the whole step as ONE launch: split-K, per-unit merge + peer push, bounded wait, final merge
+            plan3 = ShardedDecodePlan(B, Hq, Hkv, D, L, rank, world, lens, dev, dt, layout="cyclic", exchange="fused")
+
+            def sharded_fused():
+                plan3.step(Q, Kl, Vl, out)
+            for _ in range(5):
+                sharded_fused()
+            torch.cuda.synchronize()
+            plan3.exchange.check_status()
+            err3 = (out.float() - ref_out.float()).abs().max().item()
+            msf = time_region(sharded_fused, 30, True) / 30
+            res["kv_sharded_fused"] = {"world": world, "ms_per_step": msf, "speedup_vs_1gpu_step": ms / msf,
+                                       "max_abs_vs_unsharded": err3, "launches_per_step": 1, "local_splits": plan3.num_splits}
+            gs = torch.cuda.Stream()
+            gs.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(gs):
+                for _ in range(3):
+                    sharded_fused()
+            torch.cuda.current_stream().wait_stream(gs)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gr4 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr4):
+                for _ in range(10):
+                    sharded_fused()
+            torch.cuda.synchronize()
+            dist.barrier()
+            msg4 = time_region(gr4.replay, 5, True) / 50
+            plan3.exchange.check_status()
+            res["kv_sharded_fused"].update({"graph_ms_per_step": msg4, "graph_speedup_vs_1gpu_graph_step":
+                                            res.get("graph_ms_per_step", ms) / msg4})
+        except Exception as e:
+            res["kv_sharded_fused_error"] = f"{type(e).__name__}: {e}"
         try:   # the same step replayed from a CUDA graph (3 kernels + 1 all-gather per step)
             gs = torch.cuda.Stream()
             gs.wait_stream(torch.cuda.current_stream())

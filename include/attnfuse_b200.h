@@ -238,8 +238,10 @@ AF_API int af_decode_combine_gathered(const float* gathered, int32_t G, int32_t 
  * combine kernels instead of a library all-gather between them.  Every rank owns one exchange
  * buffer of af_decode_exchange_bytes() bytes, zero-initialised once, mapped into every other
  * rank's address space (e.g. torch symmetric memory); peer_bases[r] is the address of rank r's
- * buffer as seen from THIS process.  `state` is two zero-initialised uint32 in local device
- * memory (step counter, CTA counter).  All ranks must make the same sequence of calls.
+ * buffer as seen from THIS process.  `state` is zero-initialised uint32 words in local device
+ * memory: step counter, unit counter, and -- for af_decode_sharded_step -- one ticket word per
+ * (batch, kv head, chunk of 64 query heads) unit after them.  All ranks must make the same
+ * sequence of calls.
  * No counterpart in the reference, which is single-GPU. */
 typedef struct AfPeerExchange {
   int32_t world, rank;
@@ -263,6 +265,17 @@ AF_API int af_decode_combine_push(const AfDecodeParams* params, const AfPeerExch
 AF_API int af_decode_wait_merge(const AfPeerExchange* exchange, int32_t B, int32_t H_q, int32_t D,
                                 int32_t dtype, void* o, const int64_t o_stride[4],
                                 af_stream_t stream);
+
+/* The whole KV-sharded step in ONE launch (mode 3): split-K over this rank's keys; the last CTA
+ * of every (batch, kv head) unit merges the unit's splits and stores the rows into every rank's
+ * exchange buffer; the CTA that completes the last unit raises the flags; the units' last CTAs
+ * then wait (bounded, status word on expiry) for all ranks and merge from this rank's own buffer
+ * into o.  All CTAs of the launch must be resident at once (num_splits * units <= resident CTAs;
+ * AF_ERR_INVALID otherwise).  Mode 1 (push half) and mode 2 (merge half) as two launches exist for
+ * exercising several ranks on one device.  params.ws_* hold the split partials as for
+ * af_decode_split; exchange.state needs 2 + units words. */
+AF_API int af_decode_sharded_step(const AfDecodeParams* params, const AfPeerExchange* exchange, int32_t mode,
+                                  af_stream_t stream);
 
 /* Split count for a decode problem: the reference's _pick_num_splits
  * (attnfuse/runtime/flash_decode.py:69-95) re-tuned for 148 SMs.  `ragged` != 0: the

@@ -253,6 +253,56 @@ def test_peer_exchange_kernels_emulated(world):
             assert_close(out, want, torch.bfloat16, what=f"p2p exchange world={world} rank={r} step={step}")
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_single_launch_sharded_step_emulated(world):
+    """The KV-sharded step as one kernel (split-K, per-unit merge + push, wait, final merge).  With
+    one rank the whole step is a single launch on this GPU.  With more "ranks" than GPUs the launch
+    is issued in its two halves -- every rank's push half first, then every rank's merge half -- so
+    that no kernel waits for a later launch; the code of both halves is the code of the whole."""
+    from attentionfuse_b200.runtime import _lib
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode as rfd
+    B, Hq, Hkv, L, D = 4, 32, 8, 4096, 128
+    ex = _emulated_exchanges(world, B, Hq, D)
+    for step in range(3):
+        Q, K, V = qkv(2300 + step, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+        lens = torch.tensor([4096, 2048 + step, 2049, 300], dtype=torch.int32)
+        q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+        want = orc.attention(Q, K, V, kv_lens=lens)
+        plans = [ShardedDecodePlan(B, Hq, Hkv, D, L, r, world, lens, torch.device(DEV, 0), torch.bfloat16, layout="cyclic",
+                                   exchange="fused", peer_exchange=ex[r]) for r in range(world)]
+        outs = [torch.full((B, Hq, 1, D), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        kl = [cyclic_slice(k, r, world).contiguous() for r in range(world)]
+        vl = [cyclic_slice(v, r, world).contiguous() for r in range(world)]
+        before = _lib.launch_count()
+        for mode in ((3,) if world == 1 else (1, 2)):
+            for r, plan in enumerate(plans):
+                rfd(None, q, kl[r], vl[r], plan.sm_scale, 0, Hkv, outs[r], kv_lens=plan.lens_local,
+                    num_splits=plan.num_splits, workspace=plan.workspace, exchange=ex[r], exchange_mode=mode)
+        if world == 1:
+            assert _lib.launch_count() - before == 1
+        for r in range(world):
+            ex[r].check_status()
+            assert_close(outs[r], want, torch.bfloat16, what=f"single-launch step world={world} rank={r} step={step}")
+
+
+def test_single_launch_step_wait_runs_out_without_hanging():
+    """A peer that never pushes: the waiting CTAs give up after the bound, the status word is set,
+    nothing hangs, and the device stays usable."""
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode as rfd
+    world, B, Hq, Hkv, L, D = 2, 2, 8, 2, 1024, 64
+    ex = _emulated_exchanges(world, B, Hq, D, wait_cycles=2_000_000)      # ~1 ms
+    Q, K, V = qkv(2400, B, Hq, Hkv, 1, L, D, torch.float16)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    plan = ShardedDecodePlan(B, Hq, Hkv, D, L, 0, world, None, torch.device(DEV, 0), torch.float16, layout="cyclic",
+                             exchange="fused", peer_exchange=ex[0])
+    out = torch.zeros(B, Hq, 1, D, dtype=torch.float16, device=DEV)
+    rfd(None, q, cyclic_slice(k, 0, world).contiguous(), cyclic_slice(v, 0, world).contiguous(), plan.sm_scale, 0, Hkv,
+        out, kv_lens=plan.lens_local, num_splits=plan.num_splits, workspace=plan.workspace, exchange=ex[0], exchange_mode=3)
+    with pytest.raises(RuntimeError, match="did not arrive"):
+        ex[0].check_status()
+    assert_close(dense(q, k, v), orc.attention(Q, K, V), torch.float16, what="after timeout")
+
+
 def test_peer_exchange_wait_runs_out_without_hanging():
     """A rank that never pushes: the merge kernel's bounded wait ends, the status word is set, the
     host raises, and the context stays usable.  (The failure is an absent message, not a fault.)"""
