@@ -121,19 +121,14 @@ struct XLayout {
   __device__ int64_t flag_off() const { return 2 * o_floats + 2 * lse_floats; }
 };
 
-enum { XMODE_NONE = 0, XMODE_PUSH = 1, XMODE_MERGE = 2, XMODE_STEP = 3 };
-
-// XMODE (fused KV-sharded step, one launch): XMODE_PUSH -- after its partials are written, a CTA
-// takes a ticket of its (batch, kv head[, head chunk]) unit; the unit's last CTA merges the
-// unit's splits and stores the normalised rows and their log-sum-exps into slot `rank` of every
-// rank's exchange buffer (plain peer stores), and the CTA that completes the last unit raises this
-// rank's flag on every rank.  XMODE_MERGE -- that same CTA then waits (bounded) for all ranks'
-// flags and merges its unit's rows from this rank's own buffer into O.  Every CTA of the launch
-// must be resident at once (checked by the host), because the waiting CTAs keep their slots.
-template <typename T, int D, int KPW, bool ROPE, bool FUSED = false>
-__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks,
-                                                                   const AfPeerExchange x = AfPeerExchange{},
-                                                                   const int xmode = XMODE_NONE) {
+// One segment of split-K work: the query heads of chunk `chunk` of KV head (b, h_kv) against the
+// keys [lo, hi) of that head, written as un-normalised partials (m, l, acc) to the rows starting
+// at `ws_rowc` (the row of the chunk's first head).  Ends with a CTA barrier, so that segments
+// can follow one another in one CTA.
+template <typename T, int D, int KPW, bool ROPE>
+__device__ __forceinline__ void decode_segment(const AfDecodeParams& a, unsigned char* smem_raw, const int b, const int h_kv,
+                                               const int chunk, const int lo, const int hi, const int q_pos,
+                                               const int64_t ws_rowc) {
   constexpr int ROW_BYTES = D * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;       // 16-byte chunks per row
   constexpr int TILE_BYTES = DEC_BN * ROW_BYTES;
@@ -141,45 +136,15 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
   constexpr int NT_S = KPW / 8;                // score n-tiles per warp
   constexpr int NT_O = D / 8;                  // output n-tiles
   constexpr bool SPLIT_KEYS = (KPW == 16);
-
-  extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* sK = smem_raw;
   unsigned char* sV = smem_raw + DEC_STAGES * TILE_BYTES;
-
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int split = blockIdx.x;
-  // fused step: the step number this launch produces (push) or consumes (merge only); read before
-  // any CTA can complete the launch's last unit, which is what advances it
-  uint32_t xstep = 0;
-  if (FUSED) xstep = x.state[0] + ((xmode & XMODE_PUSH) ? 1u : 0u);
-  int bid = blockIdx.y;
-  const int chunk = bid % head_chunks; bid /= head_chunks;
-  const int h_kv = bid % a.H_kv;
-  const int b = bid / a.H_kv;
   const int group = a.H_q / a.H_kv;
   // First head (inside the group) of this warp's 16-row M tile.
   const int head0 = chunk * 64 + (SPLIT_KEYS ? 0 : warp * 16);
   const int key_w0 = SPLIT_KEYS ? warp * 16 : 0;   // first key of the tile this warp handles
-
-  const int len_b = a.kv_lens ? min(max(a.kv_lens[b], 0), a.N_kv) : a.N_kv;
-  // Position of the query row on the key axis.  ALiBi measures its distance from there (the
-  // reference uses the last key, attnfuse/compiler/codegen_decode.py:142-145); the causal and
-  // window masks of a single row are a range of keys.
-  const int q_pos = a.q_positions ? a.q_positions[b] : (a.q_position_p1 > 0 ? a.q_position_p1 - 1 : a.kv_offset + len_b - 1);
-  int k_lo = 0, k_hi = len_b;
-  if (a.mask_kind == AF_MASK_CAUSAL) k_hi = min(k_hi, q_pos - a.kv_offset + 1);
-  if (a.mask_kind == AF_MASK_WINDOW) {
-    k_lo = max(0, q_pos - a.window + 1 - a.kv_offset);
-    k_hi = min(k_hi, q_pos + a.window - a.kv_offset);
-  }
-  const int span = max(k_hi - k_lo, 0);
-  int split_len = (span + a.num_splits - 1) / a.num_splits;
-  split_len = ((split_len + DEC_BN - 1) / DEC_BN) * DEC_BN;
-  const int lo = k_lo + split * split_len;
-  const int hi = min(lo + split_len, k_lo + span);
   const int n_tiles = hi > lo ? (hi - lo + DEC_BN - 1) / DEC_BN : 0;
-
   const T* kbase = reinterpret_cast<const T*>(a.k) + (int64_t)b * a.k_stride[0] + (int64_t)h_kv * a.k_stride[1];
   const T* vbase = reinterpret_cast<const T*>(a.v) + (int64_t)b * a.v_stride[0] + (int64_t)h_kv * a.v_stride[1];
 
@@ -196,7 +161,6 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
     }
   };
 
-  if (!FUSED || (xmode & XMODE_PUSH)) {
   // Query fragments: rows g and g+8 of the M tile; rows past the group are zero.
   uint32_t qf[KSTEPS][4];
   {
@@ -372,7 +336,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
   cp_async_wait<0>();
   __syncthreads();
 
-  const int64_t ws_row0 = ((int64_t)split * a.B + b) * a.H_q + (int64_t)h_kv * group;
+  const int64_t ws_row0 = ws_rowc - chunk * 64;   // row of the group's head 0 in the partial arrays
   if (SPLIT_KEYS) {
     // Merge the four warps' partials (each saw a quarter of the keys) through shared memory.
     float* sm_m = reinterpret_cast<float*>(smem_raw);        // [4][16]
@@ -427,54 +391,166 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
             make_float2(o[i][2 * row], o[i][2 * row + 1]);
     }
   }
-  }   // split work
+  __syncthreads();
+}
 
+enum { XMODE_NONE = 0, XMODE_PUSH = 1, XMODE_MERGE = 2, XMODE_STEP = 3 };
+
+// Visible keys of batch entry b, [lo, lo + span), and the position of its query row.  ALiBi
+// measures its distance from q_pos (the reference uses the last key,
+// attnfuse/compiler/codegen_decode.py:142-145); the causal and window masks of a single row are a
+// range of keys.
+struct KeyRange { int lo, span, q_pos; };
+__device__ __forceinline__ KeyRange key_range(const AfDecodeParams& a, int b) {
+  const int len_b = a.kv_lens ? min(max(a.kv_lens[b], 0), a.N_kv) : a.N_kv;
+  KeyRange r;
+  r.q_pos = a.q_positions ? a.q_positions[b] : (a.q_position_p1 > 0 ? a.q_position_p1 - 1 : a.kv_offset + len_b - 1);
+  int k_lo = 0, k_hi = len_b;
+  if (a.mask_kind == AF_MASK_CAUSAL) k_hi = min(k_hi, r.q_pos - a.kv_offset + 1);
+  if (a.mask_kind == AF_MASK_WINDOW) {
+    k_lo = max(0, r.q_pos - a.window + 1 - a.kv_offset);
+    k_hi = min(k_hi, r.q_pos + a.window - a.kv_offset);
+  }
+  r.lo = k_lo;
+  r.span = max(k_hi - k_lo, 0);
+  return r;
+}
+
+// Balanced scheduling (balanced_ctas = C > 0): the 64-key tiles of all (batch, kv head, head
+// chunk) units are laid end to end -- unit u = (b * H_kv + h_kv) * head_chunks + chunk, every unit
+// at least one tile -- and CTA c takes tiles [c T / C, (c + 1) T / C): equal work per CTA whatever
+// the sequence lengths, one wave, no tail.  A CTA's share may end inside a unit and start the
+// next, so a unit is covered by a run of consecutive CTAs, and the partial of (unit u, CTA c)
+// lives in slot u + c (unique, because both only grow along the run).
+__device__ __forceinline__ int unit_tiles(const KeyRange& r) { return max(1, (r.span + DEC_BN - 1) / DEC_BN); }
+__device__ __forceinline__ int64_t total_tiles(const AfDecodeParams& a, int units_per_batch) {
+  int64_t T = 0;
+  for (int b = 0; b < a.B; ++b) T += (int64_t)unit_tiles(key_range(a, b)) * units_per_batch;
+  return T;
+}
+// CTA that holds tile index `tile` (0 <= tile < T): the c with  c T / C <= tile < (c + 1) T / C.
+__device__ __forceinline__ int cta_of_tile(int64_t tile, int64_t T, int C) {
+  int c = (int)((tile * C) / T);
+  while (c + 1 < C && ((int64_t)(c + 1) * T) / C <= tile) ++c;
+  while (c > 0 && ((int64_t)c * T) / C > tile) --c;
+  return c;
+}
+
+// Where the partial rows of one (batch, head) row live.  Classic: split s -> row s * rows + row.
+// Balanced: CTA c of the unit's run -> (unit + c) * unit_rows + head within the chunk.
+struct PartialRows {
+  int first, count;          // classic: splits 0 .. S-1; balanced: CTAs c_first .. c_last
+  int64_t base, stride;      // row index of entry i: base + i * stride
+};
+__device__ __forceinline__ PartialRows partial_rows(const AfDecodeParams& a, int head_chunks, int row, int64_t T,
+                                                    int64_t unit_start, int tiles_u, int unit) {
+  PartialRows pr;
+  const int rows = a.B * a.H_q;
+  if (a.balanced_ctas <= 0) {
+    pr.first = 0; pr.count = a.num_splits; pr.base = row; pr.stride = rows;
+  } else {
+    const int group = a.H_q / a.H_kv;
+    const int unit_rows = min(group, 64);
+    const int head_local = (row % a.H_q) % group % 64;
+    const int c0 = cta_of_tile(unit_start, T, a.balanced_ctas), c1 = cta_of_tile(unit_start + tiles_u - 1, T, a.balanced_ctas);
+    pr.first = c0; pr.count = c1 - c0 + 1;
+    pr.base = (int64_t)(unit + c0) * unit_rows + head_local; pr.stride = unit_rows;
+  }
+  return pr;
+}
+
+// Merge the partials of one row (one warp, D / 32 floats per lane): normalised values, log-sum-exp.
+template <int D>
+__device__ __forceinline__ void merge_partials(const AfDecodeParams& a, const PartialRows& pr, int lane, float (&acc)[D / 32],
+                                               float& lse) {
+  constexpr int VEC = D / 32;
+  float mstar = -INFINITY;
+  for (int i = 0; i < pr.count; ++i) mstar = fmaxf(mstar, a.ws_m[pr.base + i * pr.stride]);
+  const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  float lsum = 0.f;
+  for (int i = 0; i < pr.count; ++i) {
+    const int64_t r = pr.base + i * pr.stride;
+    const float w = expf(a.ws_m[r] - m_use);
+    lsum += w * a.ws_l[r];
+    const float* src = a.ws_acc + r * D + lane * VEC;
+    if constexpr (VEC == 4) {
+      const float4 v = *reinterpret_cast<const float4*>(src);
+      acc[0] += w * v.x; acc[1] += w * v.y; acc[2] += w * v.z; acc[3] += w * v.w;
+    } else {
+      const float2 v = *reinterpret_cast<const float2*>(src);
+      acc[0] += w * v.x; acc[1] += w * v.y;
+    }
+  }
+  const float inv = lsum == 0.f ? 0.f : 1.f / lsum;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] *= inv;
+  lse = lsum == 0.f ? -INFINITY : mstar + logf(lsum);
+}
+
+// XMODE (fused KV-sharded step, one launch): XMODE_PUSH -- after its partials are written, a CTA
+// takes a ticket of the (batch, kv head[, head chunk]) unit it worked on; the unit's last CTA
+// merges the unit's partials and stores the normalised rows and their log-sum-exps into slot
+// `rank` of every rank's exchange buffer (plain peer stores), and the CTA that completes the last
+// unit raises this rank's flag on every rank.  XMODE_MERGE -- once all of its own work is done,
+// such a CTA waits (bounded) for all ranks' flags and merges its units' rows from this rank's own
+// buffer into O.  Every CTA of the launch must be resident at once (checked by the host), because
+// the waiting CTAs keep their slots.
+template <typename T, int D, int KPW, bool ROPE, bool FUSED = false>
+__global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecodeParams a, const int head_chunks,
+                                                                   const AfPeerExchange x = AfPeerExchange{},
+                                                                   const int xmode = XMODE_NONE) {
+  constexpr int VEC = D / 32;
+  constexpr int MAX_MINE = 64;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ int s_last, s_failed, s_mine[FUSED ? MAX_MINE : 1];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int group = a.H_q / a.H_kv;
+  const int units_per_batch = a.H_kv * head_chunks;
+  const int n_units = a.B * units_per_batch;
+  const int rows = a.B * a.H_q;
+  const bool balanced = a.balanced_ctas > 0;
+  const bool do_split = !FUSED || (xmode & XMODE_PUSH);
+  // fused step: the step number this launch produces (push) or consumes (merge only); read before
+  // any CTA can complete the launch's last unit, which is what advances it
+  uint32_t xstep = 0;
+  if (FUSED) xstep = x.state[0] + ((xmode & XMODE_PUSH) ? 1u : 0u);
+  const int parity = xstep & 1;
+  int n_mine = 0;                                   // units whose rows this CTA merges at the end
   if (FUSED) {
-    constexpr int VEC = D / 32;
-    __shared__ int s_last, s_failed;
-    const int rows = a.B * a.H_q;
-    const int parity = xstep & 1;
-    const XLayout lay(x.world, rows, D);
-    const int unit = blockIdx.y;
-    const int n_units = gridDim.y;
-    const int unit_rows = min(group - chunk * 64, 64);
-    const int row0 = b * a.H_q + h_kv * group + chunk * 64;          // first (batch, head) row of the unit
-    uint32_t* tickets = x.state + 2;
-    bool last = false;
+    if (tid == 0) s_failed = 0;
+    __syncthreads();
+  }
+
+  // After the partials of `unit` are written: ticket, and for the unit's last CTA the merge of its
+  // partials with the push to every rank.  `expected` = CTAs that work on the unit.
+  auto after_unit = [&](const int unit, const int expected, const bool designated, const int64_t unit_start,
+                        const int tiles_u, const int64_t T_all) {
+    bool last = designated;                                            // merge-only launch: no ticket
     if (xmode & XMODE_PUSH) {
-      __threadfence();                                               // this CTA's partials, device-wide
+      __threadfence();                                                 // this CTA's partials, device-wide
       __syncthreads();
       if (tid == 0) {
+        uint32_t* tickets = x.state + 2;
         const uint32_t got = atomicAdd(&tickets[unit], 1u);
-        s_last = (got == (uint32_t)a.num_splits - 1u);
-        if (s_last) tickets[unit] = 0u;                              // ready for the next step
-        s_failed = 0;
+        s_last = (got == (uint32_t)expected - 1u);
+        if (s_last) tickets[unit] = 0u;                                // ready for the next step
       }
       __syncthreads();
       last = s_last != 0;
       if (last) {
-        __threadfence();                                             // the other CTAs' partials
+        __threadfence();                                               // the other CTAs' partials
+        const int chunk = unit % head_chunks, h_kv = (unit / head_chunks) % a.H_kv, b = unit / units_per_batch;
+        const int unit_rows = min(group - chunk * 64, 64);
+        const int row0 = b * a.H_q + h_kv * group + chunk * 64;
+        const XLayout lay(x.world, rows, D);
         for (int r = warp; r < unit_rows; r += DEC_THREADS / 32) {
           const int row = row0 + r;
-          float mstar = -INFINITY;
-          for (int s = 0; s < a.num_splits; ++s) mstar = fmaxf(mstar, a.ws_m[(int64_t)s * rows + row]);
-          const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
-          float acc[VEC];
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-          float lsum = 0.f;
-          for (int s = 0; s < a.num_splits; ++s) {
-            const int64_t wr = (int64_t)s * rows + row;
-            const float w = expf(a.ws_m[wr] - m_use);
-            lsum += w * a.ws_l[wr];
-            const float* src = a.ws_acc + wr * D + lane * VEC;
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] += w * src[i];
-          }
-          const float inv = lsum == 0.f ? 0.f : 1.f / lsum;
-          const float lse = lsum == 0.f ? -INFINITY : mstar + logf(lsum);
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] *= inv;
+          const PartialRows pr = partial_rows(a, head_chunks, row, T_all, unit_start, tiles_u, unit);
+          float acc[VEC], lse;
+          merge_partials<D>(a, pr, lane, acc, lse);
           for (int peer = 0; peer < x.world; ++peer) {
             float* base = reinterpret_cast<float*>(x.peer_bases[peer]);
             float* dst = base + lay.o_off(parity, x.rank, rows, D) + (int64_t)row * D + lane * VEC;
@@ -485,7 +561,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
         }
         __syncthreads();
         if (tid == 0) {
-          __threadfence_system();                                    // the unit's peer stores before the count
+          __threadfence_system();                                      // the unit's peer stores before the count
           const uint32_t done = atomicAdd(&x.state[1], 1u);
           if (done == (uint32_t)n_units - 1u) {
             x.state[1] = 0u;
@@ -499,26 +575,86 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
           }
         }
       }
-    } else {
-      last = split == 0;                                             // merge-only launch: one CTA per unit
-      if (tid == 0) s_failed = 0;
-      __syncthreads();
     }
-    if ((xmode & XMODE_MERGE) && last) {
-      const float* base = reinterpret_cast<const float*>(x.peer_bases[x.rank]);
-      const uint32_t* flags = reinterpret_cast<const uint32_t*>(base + lay.flag_off()) + parity * x.world;
-      if (tid < x.world) {
-        const long long limit = x.wait_cycles > 0 ? x.wait_cycles : (1ll << 31);
-        const long long t0 = clock64();
-        // flags only grow; a flag at or past the step (modulo wrap) means that rank's rows landed
-        while ((int32_t)(ld_acquire_sys_u32(flags + tid) - xstep) < 0) {
-          if (clock64() - t0 > limit) { s_failed = 1; break; }
+    if (last && (xmode & XMODE_MERGE)) {
+      if (n_mine < MAX_MINE) {
+        if (tid == 0) s_mine[n_mine] = unit;
+      } else if (tid == 0) {
+        s_failed = 1;                                                  // more units than the list holds
+      }
+      ++n_mine;
+    }
+  };
+
+  if (!balanced) {
+    const int split = blockIdx.x, unit = blockIdx.y;
+    const int chunk = unit % head_chunks, h_kv = (unit / head_chunks) % a.H_kv, b = unit / units_per_batch;
+    const KeyRange kr = key_range(a, b);
+    int split_len = (kr.span + a.num_splits - 1) / a.num_splits;
+    split_len = ((split_len + DEC_BN - 1) / DEC_BN) * DEC_BN;
+    const int lo = kr.lo + split * split_len;
+    const int hi = min(lo + split_len, kr.lo + kr.span);
+    if (do_split)
+      decode_segment<T, D, KPW, ROPE>(a, smem_raw, b, h_kv, chunk, lo, hi, kr.q_pos,
+                                      ((int64_t)split * a.B + b) * a.H_q + (int64_t)h_kv * group + chunk * 64);
+    if (FUSED) after_unit(unit, a.num_splits, split == 0, 0, 0, 0);
+  } else {
+    const int C = (int)gridDim.x, c = (int)blockIdx.x;
+    const int64_t T_all = total_tiles(a, units_per_batch);
+    const int64_t t_lo = ((int64_t)c * T_all) / C, t_hi = ((int64_t)(c + 1) * T_all) / C;
+    const int unit_rows_max = min(group, 64);
+    int64_t base = 0;
+    for (int b = 0; b < a.B && base < t_hi; ++b) {
+      const KeyRange kr = key_range(a, b);
+      const int tiles_u = unit_tiles(kr);
+      const int64_t b_end = base + (int64_t)tiles_u * units_per_batch;
+      if (b_end > t_lo) {
+        const int uu_first = (int)(max(t_lo - base, (int64_t)0) / tiles_u);
+        for (int uu = uu_first; uu < units_per_batch; ++uu) {
+          const int64_t unit_start = base + (int64_t)uu * tiles_u;
+          if (unit_start >= t_hi) break;
+          const int s = (int)(max(t_lo, unit_start) - unit_start), e = (int)(min(t_hi, unit_start + tiles_u) - unit_start);
+          // More CTAs than tiles: a CTA with an empty share that falls strictly inside a unit still
+          // belongs to the unit's run of CTAs (it writes an empty partial and takes its ticket);
+          // one that falls on a unit boundary belongs to no run.
+          if (e <= s && !(t_lo == t_hi && s > 0)) continue;
+          const int unit = b * units_per_batch + uu;
+          const int chunk = uu % head_chunks, h_kv = uu / head_chunks;
+          const int lo = kr.lo + s * DEC_BN, hi = min(kr.lo + e * DEC_BN, kr.lo + kr.span);
+          if (do_split)
+            decode_segment<T, D, KPW, ROPE>(a, smem_raw, b, h_kv, chunk, lo, hi, kr.q_pos, (int64_t)(unit + c) * unit_rows_max);
+          if (FUSED) {
+            const int c0 = cta_of_tile(unit_start, T_all, C), c1 = cta_of_tile(unit_start + tiles_u - 1, T_all, C);
+            after_unit(unit, c1 - c0 + 1, c == c1, unit_start, tiles_u, T_all);
+          }
         }
       }
-      __syncthreads();
-      if (s_failed) {
-        if (tid == 0 && x.status != nullptr) atomicExch(x.status, AF_STATUS_WAIT_TIMEOUT);
-      } else {
+      base = b_end;
+    }
+  }
+
+  if (FUSED && (xmode & XMODE_MERGE) && n_mine > 0) {
+    const XLayout lay(x.world, rows, D);
+    const float* base = reinterpret_cast<const float*>(x.peer_bases[x.rank]);
+    const uint32_t* flags = reinterpret_cast<const uint32_t*>(base + lay.flag_off()) + parity * x.world;
+    __syncthreads();
+    if (tid < x.world) {
+      const long long limit = x.wait_cycles > 0 ? x.wait_cycles : (1ll << 31);
+      const long long t0 = clock64();
+      // flags only grow; a flag at or past the step (modulo wrap) means that rank's rows landed
+      while ((int32_t)(ld_acquire_sys_u32(flags + tid) - xstep) < 0) {
+        if (clock64() - t0 > limit) { s_failed = 1; break; }
+      }
+    }
+    __syncthreads();
+    if (s_failed) {
+      if (tid == 0 && x.status != nullptr) atomicExch(x.status, AF_STATUS_WAIT_TIMEOUT);
+    } else {
+      for (int m = 0; m < min(n_mine, MAX_MINE); ++m) {
+        const int unit = s_mine[m];
+        const int chunk = unit % head_chunks, h_kv = (unit / head_chunks) % a.H_kv, b = unit / units_per_batch;
+        const int unit_rows = min(group - chunk * 64, 64);
+        const int row0 = b * a.H_q + h_kv * group + chunk * 64;
         for (int r = warp; r < unit_rows; r += DEC_THREADS / 32) {
           const int row = row0 + r;
           float w[32];
@@ -553,45 +689,40 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_split_kernel(const AfDecod
 // Merge the per-split partials of one (batch, head) row: one warp per row, float4 lanes.
 // Reference: attnfuse/compiler/codegen_decode.py:172-211.
 template <typename T, int D>
-__global__ void decode_combine_kernel(const AfDecodeParams a) {
+__global__ void decode_combine_kernel(const AfDecodeParams a, const int head_chunks) {
   constexpr int VEC = D / 32;   // floats per lane: 2 (D=64) or 4 (D=128)
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int rows = a.B * a.H_q;
   if (row >= rows) return;
-  const int S = a.num_splits;
-  float mstar = -INFINITY;
-  for (int s = 0; s < S; ++s) mstar = fmaxf(mstar, a.ws_m[(int64_t)s * rows + row]);
-  const float m_use = (mstar == -INFINITY) ? 0.f : mstar;
-  float acc[VEC];
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-  float lsum = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const int64_t r = (int64_t)s * rows + row;
-    const float w = expf(a.ws_m[r] - m_use);
-    lsum += w * a.ws_l[r];
-    const float* src = a.ws_acc + r * D + lane * VEC;
-    if constexpr (VEC == 4) {
-      const float4 x = *reinterpret_cast<const float4*>(src);
-      acc[0] += w * x.x; acc[1] += w * x.y; acc[2] += w * x.z; acc[3] += w * x.w;
-    } else {
-      const float2 x = *reinterpret_cast<const float2*>(src);
-      acc[0] += w * x.x; acc[1] += w * x.y;
+  const int b = row / a.H_q, h = row % a.H_q;
+  int64_t T_all = 0, unit_start = 0;
+  int tiles_u = 0, unit = 0;
+  if (a.balanced_ctas > 0) {
+    // the row's unit and its place in the tile sequence (the same walk the split kernel does)
+    const int group = a.H_q / a.H_kv, units_per_batch = a.H_kv * head_chunks;
+    const int uu = (h / group) * head_chunks + (h % group) / 64;
+    unit = b * units_per_batch + uu;
+    for (int bb = 0; bb < a.B; ++bb) {
+      const int tb = unit_tiles(key_range(a, bb));
+      if (bb < b) unit_start += (int64_t)tb * units_per_batch;
+      if (bb == b) { tiles_u = tb; unit_start += (int64_t)uu * tb; }
+      T_all += (int64_t)tb * units_per_batch;
     }
   }
-  const float inv = lsum == 0.f ? 0.f : 1.f / lsum;
-  const int b = row / a.H_q, h = row % a.H_q;
+  const PartialRows pr = partial_rows(a, head_chunks, row, T_all, unit_start, tiles_u, unit);
+  float acc[VEC], lse;
+  merge_partials<D>(a, pr, lane, acc, lse);
   if (a.o != nullptr) {
     T* dst = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) dst[(int64_t)(lane * VEC + i) * a.o_stride[3]] = Elem<T>::from_f32(acc[i] * inv);
+    for (int i = 0; i < VEC; ++i) dst[(int64_t)(lane * VEC + i) * a.o_stride[3]] = Elem<T>::from_f32(acc[i]);
   }
   if (a.partial != nullptr) {
     float* dst = a.partial + (int64_t)row * (D + 1);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) dst[lane * VEC + i] = acc[i] * inv;
-    if (lane == 0) dst[D] = lsum == 0.f ? -INFINITY : mstar + logf(lsum);
+    for (int i = 0; i < VEC; ++i) dst[lane * VEC + i] = acc[i];
+    if (lane == 0) dst[D] = lse;
   }
 }
 
@@ -626,7 +757,7 @@ int launch_split_impl(const AfDecodeParams& a, cudaStream_t st) {
   const int group = a.H_q / a.H_kv;
   const int head_chunks = (group + 63) / 64;
   const size_t smem = (size_t)2 * DEC_STAGES * DEC_BN * D * 2;
-  dim3 grid(a.num_splits, a.B * a.H_kv * head_chunks);
+  const dim3 grid = a.balanced_ctas > 0 ? dim3(a.balanced_ctas, 1) : dim3(a.num_splits, a.B * a.H_kv * head_chunks);
 #define AF_DECODE_LAUNCH(KPW, ROPE)                                                                        \
   do {                                                                                                    \
     auto kern = decode_split_kernel<T, D, KPW, ROPE>;                                                     \
@@ -646,7 +777,7 @@ int launch_split_impl(const AfDecodeParams& a, cudaStream_t st) {
 template <typename T, int D>
 int launch_combine_impl(const AfDecodeParams& a, cudaStream_t st) {
   const int rows = a.B * a.H_q;
-  decode_combine_kernel<T, D><<<(rows + 3) / 4, 128, 0, st>>>(a);
+  decode_combine_kernel<T, D><<<(rows + 3) / 4, 128, 0, st>>>(a, (a.H_q / a.H_kv + 63) / 64);
   count_launch();
   return check_cuda(cudaGetLastError(), "decode_combine launch");
 }
@@ -655,7 +786,8 @@ int validate_decode(const AfDecodeParams& a) {
   AF_REQUIRE(a.dtype == AF_F16 || a.dtype == AF_BF16, "decode kernels take f16/bf16 (got dtype %d)", a.dtype);
   AF_REQUIRE(a.D == 64 || a.D == 128, "decode kernels are instantiated for D in {64,128} (got %d)", a.D);
   AF_REQUIRE(a.B > 0 && a.H_kv > 0 && a.H_q > 0 && a.H_q % a.H_kv == 0, "bad head/batch counts");
-  AF_REQUIRE(a.num_splits >= 1, "num_splits must be >= 1");
+  AF_REQUIRE(a.num_splits >= 1 || a.balanced_ctas > 0, "num_splits must be >= 1");
+  AF_REQUIRE(a.balanced_ctas >= 0 && a.balanced_ctas <= 65535, "balanced_ctas outside [0, 65535]");
   AF_REQUIRE((int64_t)a.B * a.H_kv * ((a.H_q / a.H_kv + 63) / 64) <= 65535, "B*H_kv too large for one launch");
   AF_REQUIRE(a.ws_m && a.ws_l && a.ws_acc, "decode workspaces must be non-NULL");
   // the combine reads ws_acc rows as float4 (D = 128) / float2 (D = 64); the tensor-core split
@@ -700,6 +832,7 @@ static int static_scratch_address(float** out) {
 
 int launch_decode_static(const AfDecodeParams& in, cudaStream_t st) {
   AfDecodeParams a = in;
+  a.balanced_ctas = 0;   // the built-in scratch is laid out for the per-unit split grid
   if (a.num_splits <= 0) {
     int dev = 0, sms = 0;
     AF_CUDA_OK(cudaGetDevice(&dev));
@@ -751,7 +884,7 @@ int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
                "cos/sin rows must be 16-byte aligned");
   }
   // more than 16 query heads per KV head: tensor-bound on mma.sync, so the tcgen05 kernel takes it
-  if (decode_tc_supports(a)) return launch_decode_split_tc(a, st);
+  if (a.balanced_ctas == 0 && decode_tc_supports(a)) return launch_decode_split_tc(a, st);
   if (a.dtype == AF_F16) return a.D == 64 ? launch_split_impl<__half, 64>(a, st) : launch_split_impl<__half, 128>(a, st);
   return a.D == 64 ? launch_split_impl<__nv_bfloat16, 64>(a, st) : launch_split_impl<__nv_bfloat16, 128>(a, st);
 }
@@ -766,7 +899,7 @@ int launch_sharded_impl(const AfDecodeParams& a, const AfPeerExchange& x, int mo
   const int group = a.H_q / a.H_kv;
   const int head_chunks = (group + 63) / 64;
   const size_t smem = (size_t)2 * DEC_STAGES * DEC_BN * D * 2;
-  dim3 grid(a.num_splits, a.B * a.H_kv * head_chunks);
+  const dim3 grid = a.balanced_ctas > 0 ? dim3(a.balanced_ctas, 1) : dim3(a.num_splits, a.B * a.H_kv * head_chunks);
 #define AF_SHARDED_LAUNCH(KPW, ROPE)                                                                      \
   do {                                                                                                    \
     auto kern = decode_split_kernel<T, D, KPW, ROPE, true>;                                               \

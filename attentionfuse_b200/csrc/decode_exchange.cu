@@ -185,6 +185,7 @@ int launch_decode_combine_push(const AfDecodeParams& a, const AfPeerExchange* x,
   AF_REQUIRE(a.D == 64 || a.D == 128, "decode kernels are instantiated for D in {64,128} (got %d)", a.D);
   AF_REQUIRE(a.ws_m && a.ws_l && a.ws_acc && a.num_splits >= 1 && a.B > 0 && a.H_q > 0, "bad decode parameters");
   AF_REQUIRE(((uintptr_t)a.ws_acc & 15) == 0, "ws_acc must be 16-byte aligned");
+  AF_REQUIRE(a.balanced_ctas == 0, "the two-kernel exchange takes the per-unit split grid (balanced_ctas = 0)");
   const int rows = a.B * a.H_q;
   if (a.D == 64)
     decode_combine_push_kernel<64><<<(rows + 3) / 4, 128, 0, st>>>(a, *x);

@@ -57,11 +57,31 @@ def _pick_num_splits(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int =
     return int(_lib.load().af_decode_num_splits(B, H_q, H_kv, N_kv, _sm_count(device_index), int(ragged)))
 
 
-def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device):
+def default_balanced_ctas(B: int, H_q: int, H_kv: int, N_kv: int, device_index: int = 0) -> int:
+    """CTAs of the balanced schedule for a problem, or 0 where the split grid stays in charge.
+    Groups of up to 16 query heads per KV head (the bandwidth-bound mma.sync kernel): one wave of
+    two CTAs per SM, each with at least four 64-key tiles (measured on B16 H32/8 D128 against the
+    best split grid: 235 vs 248 us at L = 32768 with ragged lengths, 310 vs 327 us with equal ones,
+    47 vs 52 us at L = 4096).  Larger groups (MQA) run on the tensor-core split-K kernel."""
+    group = H_q // H_kv
+    if group > 16:
+        return 0
+    tiles = B * H_kv * ((N_kv + 63) // 64)
+    return max(1, min(2 * _sm_count(device_index), tiles // 4))
+
+
+def balanced_rows(B: int, H_q: int, H_kv: int, ctas: int) -> int:
+    """Partial rows of the balanced schedule: one slot of min(group, 64) rows per (unit, CTA) pair."""
+    group = H_q // H_kv
+    units = B * H_kv * ((group + 63) // 64)
+    return (units + ctas) * min(group, 64)
+
+
+def decode_workspace(num_splits: int, B: int, H_q: int, D: int, device, rows: Optional[int] = None):
     """(m, l, acc) partials carved from one allocation.  m and l each take the row count rounded
     up to 4 floats so that acc, which the kernels access with 16-byte vectors, starts on a
-    16-byte boundary for every row count."""
-    n = num_splits * B * H_q
+    16-byte boundary for every row count.  `rows` overrides num_splits * B * H_q (balanced schedule)."""
+    n = num_splits * B * H_q if rows is None else rows
     n_pad = (n + 3) & ~3
     ws = torch.empty(2 * n_pad + n * D, dtype=torch.float32, device=device)
     return ws[:n], ws[n_pad:n_pad + n], ws[2 * n_pad:]
@@ -75,7 +95,8 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      partial: Optional[torch.Tensor] = None,
                      num_splits: Optional[int] = None, workspace=None, exchange=None, exchange_mode: int = 0,
                      mask_kind: int = 0, window: int = 0, q_position: Optional[int] = None,
-                     cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                     balanced_ctas: int = 0) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
     when only the packed partial is requested)."""
     lib = _lib.load()
@@ -83,11 +104,16 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     _, H_kv, N_kv, _ = K.shape
     if V.stride() != K.stride() and (V.stride(3) != 1 or any(s % 8 for s in V.stride()[:3])):
         V = V.contiguous()
-    if num_splits is None:
+    if not balanced_ctas and num_splits is None and workspace is None:
+        dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
+        balanced_ctas = default_balanced_ctas(B, H_q, H_kv, N_kv, dev_index)
+    if balanced_ctas:
+        num_splits = 1
+    elif num_splits is None:
         dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
         num_splits = _pick_num_splits(B, H_q, H_kv, N_kv, dev_index, kv_lens is not None)
     ws_m, ws_l, ws_acc = workspace if workspace is not None else decode_workspace(
-        num_splits, B, H_q, D, Q.device)
+        num_splits, B, H_q, D, Q.device, rows=balanced_rows(B, H_q, H_kv, balanced_ctas) if balanced_ctas else None)
 
     slopes = None
     if bias_kind == 1:
@@ -106,7 +132,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     # copied afterwards: a decode step at short caches is bound by this call path
     key = (Q.dtype, Q.shape, Q.stride(), K.shape, K.stride(), V.stride(), None if out is None else out.stride(),
            float(sm_scale), int(bias_kind), int(num_splits), int(kv_offset), int(mask_kind), int(window or 0),
-           q_position, cos is not None and cos.stride(0))
+           q_position, cos is not None and cos.stride(0), int(balanced_ctas))
     template = _DECODE_TEMPLATES.get(key)
     if template is None:
         p = _lib.AfDecodeParams()
@@ -115,6 +141,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         p.sm_scale, p.bias_kind, p.num_splits = float(sm_scale), int(bias_kind), int(num_splits)
         p.q_stride, p.k_stride, p.v_stride = _lib.strides(Q), _lib.strides(K), _lib.strides(V)
         p.kv_offset = int(kv_offset)
+        p.balanced_ctas = int(balanced_ctas)
         p.mask_kind, p.window = int(mask_kind), int(window or 0)
         if q_position is not None:
             p.q_position_p1 = int(q_position) + 1

@@ -186,7 +186,7 @@ class ShardedDecodePlan:
     def __init__(self, B: int, H_q: int, H_kv: int, D: int, L_total: int, rank: int, world: int,
                  kv_lens: Optional[torch.Tensor], device, dtype, *, sm_scale: Optional[float] = None,
                  bias_kind: int = 0, slopes=None, group=None, layout: str = "contiguous",
-                 exchange: str = "nccl", peer_exchange: Optional["PeerExchange"] = None):
+                 exchange: str = "nccl", peer_exchange: Optional["PeerExchange"] = None, balanced: bool = True):
         from .flash_decode import _pick_num_splits, decode_workspace
         if exchange not in ("nccl", "p2p", "fused"):
             raise ValueError(f"unknown exchange {exchange!r}")
@@ -214,13 +214,21 @@ class ShardedDecodePlan:
         index = device.index if getattr(device, "index", None) is not None else torch.cuda.current_device()
         self.kv_offset = self.lo if layout == "contiguous" else 0
         self.num_splits = _pick_num_splits(B, H_q, H_kv, max(self.hi - self.lo, 1), index, kv_lens is not None)
+        self.balanced_ctas = 0
+        rows = None
         if self.fused:
-            # one launch for the whole step: every CTA must be resident at once (two per SM), and a
-            # rank's share of a 32k cache is short, so one wave of long CTAs beats several of short ones
-            from .flash_decode import _sm_count
+            # one launch for the whole step: every CTA must be resident at once (two per SM).  With
+            # the balanced schedule those CTAs share the tiles of all sequences equally; otherwise a
+            # rank's share of a 32k cache gets as many splits per unit as one wave holds.
+            from .flash_decode import _sm_count, balanced_rows
             units = B * H_kv * ((H_q // H_kv + 63) // 64)
-            self.num_splits = max(1, min((2 * _sm_count(index)) // units, max(1, (self.hi - self.lo) // 256)))
-        self.workspace = decode_workspace(self.num_splits, B, H_q, D, device)
+            slots = 2 * _sm_count(index)
+            if balanced:
+                self.balanced_ctas, self.num_splits = slots, 1
+                rows = balanced_rows(B, H_q, H_kv, slots)
+            else:
+                self.num_splits = max(1, min(slots // units, max(1, (self.hi - self.lo) // 256)))
+        self.workspace = decode_workspace(self.num_splits, B, H_q, D, device, rows=rows)
         self.partial = torch.empty(B, H_q, D + 1, dtype=torch.float32, device=device)
         self.gathered = torch.empty(world, B, H_q, D + 1, dtype=torch.float32, device=device)
         if exchange in ("p2p", "fused"):
@@ -237,7 +245,8 @@ class ShardedDecodePlan:
             run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, out,
                              kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
                              q_positions=self.q_positions, num_splits=self.num_splits,
-                             workspace=self.workspace, exchange=self.exchange, exchange_mode=3)
+                             workspace=self.workspace, exchange=self.exchange, exchange_mode=3,
+                             balanced_ctas=self.balanced_ctas)
             return out
         if self.exchange is not None:
             # two launches of the local decode (split, combine + push to all peers) and the

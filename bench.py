@@ -681,17 +681,20 @@ def sweep(which: str):
                 out = torch.empty_like(Q)
                 it = [0]
 
+                from attentionfuse_b200.runtime.flash_decode import default_balanced_ctas, balanced_rows
                 S = _pick_num_splits(B, Hq, Hkv, L, 0, True)
-                ws = decode_workspace(S, B, Hq, D, dev)   # allocated once, as a serving loop would
+                ctas = default_balanced_ctas(B, Hq, Hkv, L, 0)
+                ws = decode_workspace(S, B, Hq, D, dev, rows=balanced_rows(B, Hq, Hkv, ctas) if ctas else None)   # allocated once, as a serving loop would
+                sched = dict(balanced_ctas=ctas) if ctas else dict(num_splits=S)
 
                 def step():
                     Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
-                    run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens, num_splits=S, workspace=ws)
+                    run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens, workspace=ws, **sched)
                 ms = _median_ms(step)
                 nbytes = 2.0 * Hkv * D * 2 * float(lens.sum().item()) + 2.0 * B * Hq * D * 2
                 gbs = nbytes / (ms * 1e-3) / 1e9
                 print(json.dumps({"sweep": "cfg3", "H_q": Hq, "H_kv": Hkv, "L": L, "ms": round(ms, 4),
-                                  "num_splits": S, "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}), flush=True)
+                                  "schedule": f"balanced {ctas}" if ctas else f"{S} splits", "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}), flush=True)
                 if L == 32768 and Hkv == 8:
                     # one query row at the end of each sequence with a mask / rotation: the same
                     # split-K kernels, the mask as a range of keys, RoPE on the tiles in shared memory
@@ -701,8 +704,8 @@ def sweep(which: str):
                                                           ("causal+rope", 1, 0, True)):
                         def step_masked():
                             Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
-                            run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens, num_splits=S,
-                                             workspace=ws, q_positions=pos, mask_kind=mask_kind, window=window,
+                            run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens,
+                                             workspace=ws, q_positions=pos, **sched, mask_kind=mask_kind, window=window,
                                              cos=cos if rope else None, sin=sin if rope else None)
                         ms = _median_ms(step_masked)
                         keys = float(torch.clamp(lens, max=window).sum().item()) if mask_kind == 2 else float(lens.sum().item())
@@ -805,21 +808,25 @@ def bench_decode(dev, rank, world, dist_on, pk):
     Q = torch.randn(B, Hq, 1, D, generator=gen, device=dev, dtype=dt)
     out = torch.empty_like(Q)
     lens_d = lens.to(dev)
+    from attentionfuse_b200.runtime.flash_decode import default_balanced_ctas, balanced_rows
     S = _pick_num_splits(B, Hq, Hkv, L, dev.index or 0, True)
-    ws = decode_workspace(S, B, Hq, D, dev)
+    ctas = default_balanced_ctas(B, Hq, Hkv, L, dev.index or 0)      # the schedule the public call picks
+    ws = decode_workspace(S, B, Hq, D, dev, rows=balanced_rows(B, Hq, Hkv, ctas) if ctas else None)
+    sched = dict(balanced_ctas=ctas) if ctas else dict(num_splits=S)
     sm_scale = 1.0 / D ** 0.5
     bytes_step = 2.0 * Hkv * D * 2 * float(lens.sum()) + 2.0 * B * Hq * D * 2
     it = [0]
 
     def step():
         Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
-        run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, num_splits=S, workspace=ws)
+        run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, workspace=ws, **sched)
 
     for _ in range(5):
         step()
     ms = time_region(step, 30, dist_on) / 30
     gbs = bytes_step / (ms * 1e-3) / 1e9
-    res = {"gbs_per_gpu": gbs, "ms_per_step": ms, "bytes_per_step": bytes_step, "num_splits": S,
+    res = {"gbs_per_gpu": gbs, "ms_per_step": ms, "bytes_per_step": bytes_step,
+           "schedule": f"balanced, {ctas} CTAs" if ctas else f"{S} splits per (batch, kv head)",
            "frac_of_measured_hbm": gbs / pk["hbm_gbs"], "frac_of_nominal_8000": gbs / 8000.0,
            "config": "B16 H32/8 D128 L32768 bf16, lengths U[L/2, L], 3 rotating caches (2.1 GB each)"}
     # CUDA-graph replay of the two launches (launch overhead matters at this step time)
@@ -828,12 +835,12 @@ def bench_decode(dev, rank, world, dist_on, pk):
         Kc, Vc = caches[0]
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
-            run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, num_splits=S, workspace=ws)
+            run_flash_decode(None, Q, Kc, Vc, sm_scale, 0, Hkv, out, kv_lens=lens_d, workspace=ws, **sched)
             torch.cuda.synchronize()
             with torch.cuda.graph(gr, stream=s):
                 for i in range(n_buf):
                     run_flash_decode(None, Q, caches[i][0], caches[i][1], sm_scale, 0, Hkv, out, kv_lens=lens_d,
-                                     num_splits=S, workspace=ws)
+                                     workspace=ws, **sched)
         torch.cuda.synchronize()
         msg = time_region(gr.replay, 10, dist_on) / (10 * n_buf)
         res["graph_gbs_per_gpu"] = bytes_step / (msg * 1e-3) / 1e9
@@ -849,7 +856,7 @@ def bench_decode(dev, rank, world, dist_on, pk):
         plan = ShardedDecodePlan(B, Hq, Hkv, D, L, rank, world, lens, dev, dt, layout="cyclic")
         ref_out = torch.empty_like(Q)
         run_flash_decode(None, Q, caches[0][0], caches[0][1], sm_scale, 0, Hkv, ref_out, kv_lens=lens_d,
-                         num_splits=S, workspace=ws)
+                         workspace=ws, **sched)
 
         def sharded():
             plan.step(Q, Kl, Vl, out)

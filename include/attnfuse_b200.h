@@ -166,6 +166,13 @@ typedef struct AfDecodeParams {
   int32_t rope;
   int32_t q_position_p1;        /* query position + 1; 0 = not given                        */
   const void* cos; const void* sin; int64_t rope_stride_n;
+  /* Balanced scheduling: > 0 launches that many CTAs, each taking an equal share of the 64-key
+   * tiles of all sequences laid end to end (one wave, equal work whatever the lengths), instead
+   * of num_splits CTAs per (batch, kv head).  The workspaces then hold
+   * (units + balanced_ctas) * min(group, 64) rows, units = B * H_kv * ceil(group / 64),
+   * group = H_q / H_kv; num_splits is ignored.  The reference splits every sequence into the
+   * same number of pieces (attnfuse/runtime/flash_decode.py:114-131). */
+  int32_t balanced_ctas;
 } AfDecodeParams;
 
 /* Replaces the forward launch in run_attention (attnfuse/runtime/dispatch.py:196-214)

@@ -253,8 +253,50 @@ def test_peer_exchange_kernels_emulated(world):
             assert_close(out, want, torch.bfloat16, what=f"p2p exchange world={world} rank={r} step={step}")
 
 
+@pytest.mark.parametrize("ctas", [1, 7, 100, 296, 1000])
+@pytest.mark.parametrize("geom", [(32, 8, 128), (64, 1, 128), (9, 3, 128), (8, 2, 64), (80, 1, 64)],
+                         ids=lambda g: f"{g[0]}q{g[1]}kv_d{g[2]}")
+def test_balanced_schedule(ctas, geom):
+    """balanced_ctas: every CTA takes an equal share of the 64-key tiles of all sequences laid end to
+    end, so a share may end inside one (batch, kv head) unit and start the next.  Ragged lengths
+    (one sequence empty, one of a single key), CTA counts below and far above the tile count."""
+    Hq, Hkv, D = geom
+    B, L, dtype = 5, 2500, torch.bfloat16
+    Q, K, V = qkv(2600 + Hq, B, Hq, Hkv, 1, L, D, dtype)
+    lens = torch.tensor([2500, 1, 1300, 0, 777], dtype=torch.int32)
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    k[3] = float("nan"); v[3] = float("nan")          # the empty sequence's cache must not be read into the result
+    out = torch.full_like(q, float("nan"))
+    run_flash_decode(None, q, k, v, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens.to(DEV), balanced_ctas=ctas)
+    want = orc.attention(Q, K, V, kv_lens=lens)
+    assert_close(out, want, dtype, what=f"balanced {geom} ctas={ctas}")
+
+
+@pytest.mark.parametrize("variant", ["causal_alibi", "window_rope"])
+def test_balanced_schedule_with_masks_and_rotation(variant):
+    Hq, Hkv, D, B, L, W, dtype = 16, 4, 128, 3, 3000, 700, torch.bfloat16
+    p = 2345
+    Q, K, V = qkv(2700, B, Hq, Hkv, 1, L, D, dtype)
+    kw, okw = {}, {"q_offset": p, "causal": "causal" in variant}
+    if "rope" in variant:
+        cos, sin = orc.build_rope_cache(L, D, 500000.0, dtype)
+        kw.update(cos=cos.to(DEV), sin=sin.to(DEV)); okw.update(cos=cos, sin=sin)
+    slopes = None
+    if "alibi" in variant:
+        slopes = _alibi_slopes(Hq, "cpu", str(dtype))
+        okw.update(slopes=slopes, q_positions=torch.full((B,), p))
+    if "window" in variant:
+        okw["window"] = W
+    out = torch.empty(B, Hq, 1, D, dtype=dtype, device=DEV)
+    run_flash_decode(None, Q.to(DEV), K.to(DEV), V.to(DEV), 1.0 / D ** 0.5, 1 if slopes is not None else 0, Hkv, out,
+                     alibi_slopes=slopes, q_position=p, mask_kind=1 if "causal" in variant else 2, window=W,
+                     balanced_ctas=148, **kw)
+    assert_close(out, orc.attention(Q, K, V, **okw), dtype, what=f"balanced {variant}")
+
+
+@pytest.mark.parametrize("balanced", [False, True], ids=["split_grid", "balanced"])
 @pytest.mark.parametrize("world", [1, 2, 8])
-def test_single_launch_sharded_step_emulated(world):
+def test_single_launch_sharded_step_emulated(world, balanced):
     """The KV-sharded step as one kernel (split-K, per-unit merge + push, wait, final merge).  With
     one rank the whole step is a single launch on this GPU.  With more "ranks" than GPUs the launch
     is issued in its two halves -- every rank's push half first, then every rank's merge half -- so
@@ -269,7 +311,7 @@ def test_single_launch_sharded_step_emulated(world):
         q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
         want = orc.attention(Q, K, V, kv_lens=lens)
         plans = [ShardedDecodePlan(B, Hq, Hkv, D, L, r, world, lens, torch.device(DEV, 0), torch.bfloat16, layout="cyclic",
-                                   exchange="fused", peer_exchange=ex[r]) for r in range(world)]
+                                   exchange="fused", peer_exchange=ex[r], balanced=balanced) for r in range(world)]
         outs = [torch.full((B, Hq, 1, D), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
         kl = [cyclic_slice(k, r, world).contiguous() for r in range(world)]
         vl = [cyclic_slice(v, r, world).contiguous() for r in range(world)]
@@ -277,7 +319,8 @@ def test_single_launch_sharded_step_emulated(world):
         for mode in ((3,) if world == 1 else (1, 2)):
             for r, plan in enumerate(plans):
                 rfd(None, q, kl[r], vl[r], plan.sm_scale, 0, Hkv, outs[r], kv_lens=plan.lens_local,
-                    num_splits=plan.num_splits, workspace=plan.workspace, exchange=ex[r], exchange_mode=mode)
+                    num_splits=plan.num_splits, workspace=plan.workspace, exchange=ex[r], exchange_mode=mode,
+                    balanced_ctas=plan.balanced_ctas)
         if world == 1:
             assert _lib.launch_count() - before == 1
         for r in range(world):

@@ -15,7 +15,7 @@ import pytest
 import torch
 
 from attentionfuse_b200.runtime import _lib
-from attentionfuse_b200.runtime.flash_decode import run_flash_decode
+from attentionfuse_b200.runtime.flash_decode import run_flash_decode, _pick_num_splits
 from oracle import attention_oracle as orc
 from tests._util import assert_close, qkv
 
@@ -53,7 +53,10 @@ def test_static_scratch_decode_matches_regular_path_twice():
         lens = torch.randint(L // 2, L + 1, (B,), generator=g, dtype=torch.int32)
         q, k, v, lens_d = Q.to(DEV), K.to(DEV), V.to(DEV), lens.to(DEV)
         want = torch.empty_like(q)
-        run_flash_decode(None, q, k, v, 1.0 / D ** 0.5, 0, Hkv, want, kv_lens=lens_d)
+        # the regular entry points with torch-allocated workspaces, on the same split grid the
+        # allocation-free entry point uses (the public call's default is the balanced schedule)
+        run_flash_decode(None, q, k, v, 1.0 / D ** 0.5, 0, Hkv, want, kv_lens=lens_d,
+                         num_splits=_pick_num_splits(B, Hq, Hkv, L, 0, True))
         got = torch.full_like(q, float("nan"))
         rc = decode_static(q, k, v, got, kv_lens=lens_d)
         assert rc == 0, _lib.last_error()
