@@ -83,7 +83,8 @@ def sharded_decode(Q: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor
     key range; kv_lens (B,) are GLOBAL valid lengths (None: all L_total keys valid).
     `local_partial`, `combine` and `all_gather` are injection points for CPU tests of the host
     logic; by default they are the CUDA kernels and torch.distributed.all_gather_into_tensor.
-    Raises RuntimeError if a gathered LSE is NaN (a rank produced garbage).
+    The gathered partials are not inspected here (that would synchronise every step);
+    `check_gathered(gather_buffer)` is the debug aid that raises on a NaN log-sum-exp.
     """
     import torch.distributed as dist
     B, H_q, _, D = Q.shape
@@ -237,7 +238,16 @@ class ShardedDecodePlan:
             elif world > 1:
                 self.exchange = PeerExchange(world, rank, B, H_q, D, device, group=group)
 
+    def check(self) -> None:
+        """Raise if a bounded wait of the peer exchange ran out since the last check (synchronises;
+        call it at the caller's own sync points).  After a timed-out step `out` is undefined: the
+        merge does not run when a peer's rows have not arrived."""
+        if self.exchange is not None:
+            self.exchange.check_status()
+
     def step(self, Q: torch.Tensor, K_local: torch.Tensor, V_local: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """One decode step; returns `out`.  With a peer exchange (`p2p`, `fused`) a peer that does not
+        deliver within the wait bound leaves `out` unwritten and sets a status word: see `check()`."""
         import torch.distributed as dist
         from .flash_decode import run_flash_decode, combine_gathered
         if self.exchange is not None and self.fused:

@@ -36,8 +36,9 @@ def test_struct_layouts_match_the_header(tmp_path):
         '#include <stdio.h>\n#include <stddef.h>\n#include "attnfuse_b200.h"\n'
         "int main(void) {\n"
         '  printf("%zu %zu %zu %zu\\n", sizeof(AfProblem), sizeof(AfFwdParams), sizeof(AfBwdParams), sizeof(AfDecodeParams));\n'
-        '  printf("%zu %zu %zu %zu %zu\\n", offsetof(AfProblem, q), offsetof(AfProblem, status), offsetof(AfFwdParams, workspace),\n'
-        "         offsetof(AfBwdParams, dv), offsetof(AfDecodeParams, partial));\n"
+        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", offsetof(AfProblem, q), offsetof(AfProblem, status), offsetof(AfFwdParams, workspace),\n'
+        "         offsetof(AfBwdParams, dv), offsetof(AfDecodeParams, partial), offsetof(AfProblem, q_bits),\n"
+        "         offsetof(AfBwdParams, dq_accum), offsetof(AfDecodeParams, balanced_ctas));\n"
         "  return 0;\n}\n")
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
@@ -46,7 +47,8 @@ def test_struct_layouts_match_the_header(tmp_path):
     assert sizes[:4] == [C.sizeof(_lib.AfProblem), C.sizeof(_lib.AfFwdParams), C.sizeof(_lib.AfBwdParams),
                          C.sizeof(_lib.AfDecodeParams)]
     assert sizes[4:] == [_lib.AfProblem.q.offset, _lib.AfProblem.status.offset, _lib.AfFwdParams.workspace.offset,
-                         _lib.AfBwdParams.dv.offset, _lib.AfDecodeParams.partial.offset]
+                         _lib.AfBwdParams.dv.offset, _lib.AfDecodeParams.partial.offset, _lib.AfProblem.q_bits.offset,
+                         _lib.AfBwdParams.dq_accum.offset, _lib.AfDecodeParams.balanced_ctas.offset]
 
 
 def test_host_only_entry_points():
