@@ -63,8 +63,17 @@ constexpr float kRowSumBound = 8192.f;
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
   static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;     // one Q, K or V tile
-  static constexpr int STAGES = (D == 128) ? 3 : 4;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 /*align*/ + 1536 /*barriers, exchange*/;
+  // K tiles are consumed early (S runs up to two tiles ahead of the softmax group), V tiles late
+  // (after the tile's softmax), so a V slot freed by P.V of tile j is not needed before tile j+2
+  // has gone through the softmax group: two V stages suffice at head dim 128, and the tile they
+  // leave free stages the output rows for a TMA store.
+  static constexpr int STAGES = (D == 128) ? 3 : 4;            // K ring
+  static constexpr int STAGES_V = (D == 128) ? 2 : 4;          // V ring
+  // 8 regions [half][row quadrant] of 32 rows; a row of a region holds D/2 elements and sits on
+  // the 128-byte pitch of the swizzle whether it fills it (D = 128) or not (D = 64)
+  static constexpr int O_STAGE_BYTES = 8 * 32 * 128;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + STAGES + STAGES_V) + O_STAGE_BYTES + 1024 /*align*/ +
+                                    1536 /*barriers, exchange*/;
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + D;   // one O per half of the key columns
 };
@@ -86,6 +95,8 @@ struct Barriers {
   uint32_t pair_flag[2][8];   // hand-shake counts of the softmax warps, two slots by parity of the count
   float xchg[SOFTMAX_THREADS];   // reference maximum / row sum exchange between the two halves of a row
 };
+
+static_assert(sizeof(Barriers) <= 1536, "Cfg::SMEM_BYTES reserves 1536 bytes for the barriers and the exchange");
 
 struct TcArgs {
   AfFwdParams a;
@@ -193,6 +204,26 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
   it.m0 = m_blk * BM;
   it.walk = make_walk(p, args, m_blk, it.h);
   return true;
+}
+
+// Position of a role in the CTA's sequence of key tiles (items without key tiles are skipped):
+// gg = running tile count, qi = running count of items with tiles, j = tile within the item.
+struct TileCursor {
+  Item it;
+  int round, j, gg, qi;
+};
+__device__ __forceinline__ void cursor_init(TileCursor& c) {
+  c.round = -1; c.j = 0; c.gg = -1; c.qi = -1;
+  c.it.walk.n_tiles = 0;
+}
+template <int EMASK, bool SPLIT>
+__device__ __forceinline__ bool cursor_next(const TcArgs& args, TileCursor& c) {
+  if (c.j + 1 < c.it.walk.n_tiles) { ++c.j; ++c.gg; return true; }
+  for (;;) {
+    ++c.round;
+    if (!get_item<EMASK, SPLIT>(args, c.round, c.it)) return false;
+    if (c.it.walk.n_tiles > 0) { c.j = 0; ++c.gg; ++c.qi; return true; }
+  }
 }
 
 template <typename T> struct Pack2;
@@ -344,9 +375,10 @@ __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk
 template <typename T, int D, int ROPE, int EMASK, bool ALIBI, bool SPLIT>
 __global__ void __launch_bounds__(ROPE == ROPE_FUSED ? 384 : 352, 1)
 fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
-                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                   const __grid_constant__ CUtensorMap tmap_o) {
   using C = Cfg<D>;
-  constexpr int STAGES = C::STAGES;
+  constexpr int STAGES = C::STAGES, STAGES_V = C::STAGES_V;
   constexpr bool ROT_K = (ROPE == ROPE_FUSED);
   constexpr int AB_FMT = (Elem<T>::code == AF_BF16) ? 1 : 0;
   constexpr uint32_t IDESC_QK = umma_idesc_f16(AB_FMT, BM, BN, 0, 0);
@@ -361,7 +393,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   const uint32_t sQ = smem_base;
   const uint32_t sK0 = sQ + C::TILE_BYTES;
   const uint32_t sV0 = sK0 + STAGES * C::TILE_BYTES;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::TILE_BYTES * (1 + 2 * STAGES));
+  const uint32_t sO = sV0 + STAGES_V * C::TILE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + C::TILE_BYTES * (1 + STAGES + STAGES_V) + C::O_STAGE_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -408,38 +441,58 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
-      Item it;
-      int g = 0, qi = 0;
-      bool ok = true;
-      for (int round = 0; ok && get_item<EMASK, SPLIT>(args, round, it); ++round) {
-        const int n_tiles = it.walk.n_tiles;
-        if (n_tiles == 0) continue;
-        // the single Q buffer is free once the last S product of the previous item has run
-        if (qi > 0 && !mbar_wait(&bars->q_empty, (qi - 1) & 1, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
+      tma_prefetch_desc(&tmap_o);
+      // Two cursors over the same tile sequence: K runs one tile ahead of V, so that a wait for
+      // a V slot (free only after the P.V product two tiles back) never holds up a K load.
+      TileCursor ck, cv;
+      cursor_init(ck);
+      cursor_init(cv);
+      auto load_k = [&]() -> bool {
+        if (ck.j == 0) {
+          // the single Q buffer is free once the last S product of the previous item has run
+          if (ck.qi > 0 && !mbar_wait(&bars->q_empty, (ck.qi - 1) & 1, abort_flag)) return false;
+          mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
+#pragma unroll
+          for (int pn = 0; pn < C::PANELS; ++pn)
+            tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, ck.it.m0, ck.it.h, ck.it.b);
+        }
+        const int s = ck.gg % STAGES;
+        const uint32_t par = ((ck.gg / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
+        unsigned char* dk = smem + C::TILE_BYTES * (1 + s);
+        if (ck.gg >= STAGES && !mbar_wait(&bars->k_empty[s], par, abort_flag)) return false;
+        mbar_arrive_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+        const int key0 = ck.it.walk.key0(ck.j);
 #pragma unroll
         for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, it.m0, it.h, it.b);
-        for (int j = 0; j < n_tiles; ++j) {
-          const int gg = g + j;
-          const int s = gg % STAGES;
-          const uint32_t par = ((gg / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
-          const int key0 = it.walk.key0(j);
-          unsigned char* dk = smem + C::TILE_BYTES * (1 + s);
-          unsigned char* dv = smem + C::TILE_BYTES * (1 + STAGES + s);
-          if (gg >= STAGES && !mbar_wait(&bars->k_empty[s], par, abort_flag)) { ok = false; break; }
-          mbar_arrive_expect_tx(&bars->k_full[s], C::TILE_BYTES);
+          tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, ck.it.h_kv, ck.it.b);
+        return true;
+      };
+      auto load_v = [&]() -> bool {
+        const int s = cv.gg % STAGES_V;
+        const uint32_t par = ((cv.gg / STAGES_V) & 1) ^ 1;
+        unsigned char* dv = smem + C::TILE_BYTES * (1 + STAGES + s);
+        if (cv.gg >= STAGES_V && !mbar_wait(&bars->v_empty[s], par, abort_flag)) return false;
+        mbar_arrive_expect_tx(&bars->v_full[s], C::TILE_BYTES);
+        const int key0 = cv.it.walk.key0(cv.j);
 #pragma unroll
-          for (int pn = 0; pn < C::PANELS; ++pn)
-            tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, it.h_kv, it.b);
-          if (gg >= STAGES && !mbar_wait(&bars->v_empty[s], par, abort_flag)) { ok = false; break; }
-          mbar_arrive_expect_tx(&bars->v_full[s], C::TILE_BYTES);
-#pragma unroll
-          for (int pn = 0; pn < C::PANELS; ++pn)
-            tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, it.h_kv, it.b);
+        for (int pn = 0; pn < C::PANELS; ++pn)
+          tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, cv.it.h_kv, cv.it.b);
+        return true;
+      };
+      bool more_k = cursor_next<EMASK, SPLIT>(args, ck);
+      bool more_v = cursor_next<EMASK, SPLIT>(args, cv);
+      bool ok = true;
+      if (more_k) {
+        ok = load_k();
+        more_k = ok && cursor_next<EMASK, SPLIT>(args, ck);
+      }
+      while (ok && more_v) {
+        if (more_k) {
+          if (!load_k()) break;
+          more_k = cursor_next<EMASK, SPLIT>(args, ck);
         }
-        g += n_tiles;
-        ++qi;
+        if (!load_v()) break;
+        more_v = cursor_next<EMASK, SPLIT>(args, cv);
       }
     }
   } else if (warp == WARP_QK) {
@@ -494,8 +547,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         if (n_tiles == 0) continue;
         for (int j = 0; j < n_tiles; ++j) {
           const int gg = g + j;
-          const int s = gg % STAGES, t = gg & 1;
-          if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
+          const int s = gg % STAGES_V, t = gg & 1;
+          if (!mbar_wait(&bars->v_full[s], (gg / STAGES_V) & 1, abort_flag)) { ok = false; break; }
           // the first P.V product of an item overwrites O: the previous item's rows must be read out
           if (j == 0 && qi > 0 && !mbar_wait(&bars->o_free, (qi - 1) & 1, abort_flag)) { ok = false; break; }
           const uint64_t vdesc = desc_v0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
@@ -660,8 +713,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           // Split-K decode: cache rows past the valid length hold whatever the allocation held
           // (TMA zero-fills only past the tensor's extent) and 0 * NaN would poison O, so the
           // softmax threads clear those V rows of the stage before they release P.
-          const int s = gg % STAGES;
-          if (!mbar_wait(&bars->v_full[s], (gg / STAGES) & 1, abort_flag)) { alive = false; break; }
+          const int s = gg % STAGES_V;
+          if (!mbar_wait(&bars->v_full[s], (gg / STAGES_V) & 1, abort_flag)) { alive = false; break; }
           // each half clears the rows its own P.V product reads (keys [64 half, 64 half + 64))
           const int first = max(n_kv - key0, half * HALF_COLS), last = (half + 1) * HALF_COLS;
           const uint32_t v_tile = sV0 + s * C::TILE_BYTES;
@@ -677,29 +730,43 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         mbar_arrive(&bars->p_full[t][half]);
       }
 
-      // Epilogue.  The two halves of a row meet: they exchange (reference maximum, row sum), each
-      // merges its half of the output columns from both accumulators,
-      //   O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)),  m = max(m_0, m_1),
-      // hands the accumulators back to the MMA warp and stores; L = m + log(l).
+      // Epilogue.  The two halves of a row meet and each merges its half of the output columns
+      // from both accumulators,
+      //   O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)),  m = max(m_0, m_1);
+      // L = m + log(l).  The exchange runs while the last P.V product is still in flight: half 1
+      // hands (m_1, l_1) to half 0, which returns the two accumulator weights c_h = 2^(m_h - m) / l
+      // through the same words (two hand-shakes; the next item's words are written only after
+      // this item's have been read).
       if (!alive) break;
+      float c0 = 0.f, c1 = 0.f, m_all = 0.f, l_sum = 0.f;
+      if (half == 1) {
+        bars->xchg[rtid] = m_ref;
+        bars->xchg[BM + rtid] = l_part;
+      }
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      if (half == 0) {
+        const float m_other = bars->xchg[rtid], l_other = bars->xchg[BM + rtid];
+        m_all = fmaxf(m_ref, m_other);
+        const float w_mine = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_all);
+        const float w_other = (m_other == -INFINITY) ? 0.f : ex2_approx(m_other - m_all);
+        l_sum = l_part * w_mine + l_other * w_other;
+        // split-K decode keeps the partial un-normalised for the combine kernel
+        const float inv = SPLIT ? 1.f : 1.f / ((l_sum == 0.f) ? 1.f : l_sum);
+        c0 = w_mine * inv;
+        c1 = w_other * inv;
+        bars->xchg[rtid] = c0;
+        bars->xchg[BM + rtid] = c1;
+      }
+      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
+      if (half == 1) {
+        c0 = bars->xchg[rtid];
+        c1 = bars->xchg[BM + rtid];
+      }
       if (n_tiles > 0) {
         const int gl = g + n_tiles - 1;
         if (!mbar_wait(&bars->pv_done[gl & 1], (gl >> 1) & 1, abort_flag)) { alive = false; break; }
         tc_fence_after_sync();
       }
-      bars->xchg[tid] = m_ref;
-      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
-      const float m_other = bars->xchg[tid ^ BM];
-      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
-      bars->xchg[tid] = l_part;
-      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
-      const float l_other = bars->xchg[tid ^ BM];
-      if (!pair_sync(bars, warp, lane, pair_count, abort_flag)) { alive = false; break; }
-      const float m_all = fmaxf(m_ref, m_other);
-      const float w_mine = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_all);
-      const float w_other = (m_other == -INFINITY) ? 0.f : ex2_approx(m_other - m_all);
-      const float l_sum = l_part * w_mine + l_other * w_other;
-      const float w0 = half == 0 ? w_mine : w_other, w1 = half == 0 ? w_other : w_mine;
       float o[D / 2];
       if (n_tiles > 0) {
         uint32_t o0[D / 2], o1[D / 2];
@@ -712,7 +779,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         tc_fence_before_sync();
         mbar_arrive(&bars->o_free);
 #pragma unroll
-        for (int i = 0; i < D / 2; ++i) o[i] = __uint_as_float(o0[i]) * w0 + __uint_as_float(o1[i]) * w1;
+        for (int i = 0; i < D / 2; ++i) o[i] = __uint_as_float(o0[i]) * c0 + __uint_as_float(o1[i]) * c1;
       } else {
 #pragma unroll
         for (int i = 0; i < D / 2; ++i) o[i] = 0.f;
@@ -730,30 +797,41 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           }
         }
       } else {
-        const float safe_l = (l_sum == 0.f) ? 1.f : l_sum;
-        const float inv = 1.f / safe_l;
-        T* orow = reinterpret_cast<T*>(a.o) + (int64_t)b * a.o_stride[0] + (int64_t)h * a.o_stride[1] +
-                  (int64_t)row * a.o_stride[2] + half * (D / 2);
-        if (row < p.N_q) {
+        // The rows go out through shared memory: a thread owns one row, so direct stores touch 32
+        // different 128-byte lines per instruction (measured: 3300 cycles per item).  Each warp
+        // stages its 32 rows of D bytes in the 128-byte swizzle of the output tensor map --
+        // conflict-free 16-byte stores -- and one lane sends them with a TMA store, which also
+        // drops the rows past N_q.  The staging region is the warp's own; before it is written
+        // again the previous store must have read it.
+        const uint32_t stage = sO + (uint32_t)((half * 4 + (warp & 3)) * 32 * 128);
+        if (lane == 0) bulk_wait_read_all();
+        __syncwarp();
 #pragma unroll
-          for (int q8 = 0; q8 < D / 16; ++q8) {
-            uint4 v;
-            v.x = Pack2<T>::run(o[q8 * 8 + 0] * inv, o[q8 * 8 + 1] * inv);
-            v.y = Pack2<T>::run(o[q8 * 8 + 2] * inv, o[q8 * 8 + 3] * inv);
-            v.z = Pack2<T>::run(o[q8 * 8 + 4] * inv, o[q8 * 8 + 5] * inv);
-            v.w = Pack2<T>::run(o[q8 * 8 + 6] * inv, o[q8 * 8 + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + q8 * 8) = v;
-          }
-          if (a.lse != nullptr && half == 0)
-            a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
-                m_all * kLn2 + logf(safe_l);
+        for (int q8 = 0; q8 < D / 16; ++q8) {
+          uint4 v;
+          v.x = Pack2<T>::run(o[q8 * 8 + 0], o[q8 * 8 + 1]);
+          v.y = Pack2<T>::run(o[q8 * 8 + 2], o[q8 * 8 + 3]);
+          v.z = Pack2<T>::run(o[q8 * 8 + 4], o[q8 * 8 + 5]);
+          v.w = Pack2<T>::run(o[q8 * 8 + 6], o[q8 * 8 + 7]);
+          sts128(stage + (uint32_t)(lane * 128 + ((q8 ^ (lane & 7)) << 4)), v);
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int row0 = m0 + (warp & 3) * 32;
+        if (lane == 0 && row0 < p.N_q) {
+          tma_store_4d(&tmap_o, stage, half * (D / 2), row0, h, b);
+          bulk_commit_group();
+        }
+        if (a.lse != nullptr && half == 0 && row < p.N_q)
+          a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
+              m_all * kLn2 + logf((l_sum == 0.f) ? 1.f : l_sum);
       }
       if (n_tiles > 0) {
         g += n_tiles;
         ++qi;
       }
     }
+    if (lane == 0) bulk_wait_all();   // the staged rows must have left shared memory before the CTA exits
   } else if (ROT_K && warp == WARP_ROTATE) {
     // ============================== K rotation warp ==============================
     // One warp; each thread rotates four key rows of the tile.
@@ -798,7 +876,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
 // ---------------------------------------------------------------------------------------
 template <typename T, int D, int ROPE, int EMASK, bool ALIBI, bool SPLIT = false>
 int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                    cudaStream_t st) {
+                    const CUtensorMap& mo, cudaStream_t st) {
   auto kern = fwd_tcgen05_kernel<T, D, ROPE, EMASK, ALIBI, SPLIT>;
   constexpr int smem = Cfg<D>::SMEM_BYTES;
   static bool configured = false;   // benign race: the attribute call is idempotent
@@ -806,7 +884,7 @@ int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 384 : 352, smem, st>>>(args, mq, mk, mv);
+  kern<<<(unsigned)args.grid_ctas, ROPE == ROPE_FUSED ? 384 : 352, smem, st>>>(args, mq, mk, mv, mo);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_tcgen05 launch");
 }
@@ -815,10 +893,10 @@ int launch_instance(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap
 // per-(D, RoPE) translation units so that they compile in parallel.
 template <typename T, int D, int ROPE>
 int launch_composition(const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                       cudaStream_t st) {
+                       const CUtensorMap& mo, cudaStream_t st) {
   const AfProblem& p = args.a.p;
   if (args.num_splits > 0) {   // split-K decode: dense, no bias, no rotation (one extra instantiation)
-    if constexpr (ROPE == ROPE_NONE) return launch_instance<T, D, ROPE_NONE, EMASK_NONE, false, true>(args, mq, mk, mv, st);
+    if constexpr (ROPE == ROPE_NONE) return launch_instance<T, D, ROPE_NONE, EMASK_NONE, false, true>(args, mq, mk, mv, mo, st);
     else return fail(AF_ERR_UNSUPPORTED, "split-K decode takes no rotation");
   }
   int em = p.mask_kind == AF_MASK_CAUSAL ? EMASK_CAUSAL : p.mask_kind == AF_MASK_WINDOW ? EMASK_WINDOW : EMASK_NONE;
@@ -827,33 +905,33 @@ int launch_composition(const TcArgs& args, const CUtensorMap& mq, const CUtensor
   if (em == EMASK_BITS) {
     // block lists never come with rotation (the block-sparse call has no cos / sin)
     if constexpr (ROPE == ROPE_NONE) {
-      return alibi ? launch_instance<T, D, ROPE_NONE, EMASK_BITS, true>(args, mq, mk, mv, st)
-                   : launch_instance<T, D, ROPE_NONE, EMASK_BITS, false>(args, mq, mk, mv, st);
+      return alibi ? launch_instance<T, D, ROPE_NONE, EMASK_BITS, true>(args, mq, mk, mv, mo, st)
+                   : launch_instance<T, D, ROPE_NONE, EMASK_BITS, false>(args, mq, mk, mv, mo, st);
     } else {
       return fail(AF_ERR_UNSUPPORTED, "block lists with element bit matrices take no rotation");
     }
   }
   switch (em * 2 + (alibi ? 1 : 0)) {
-    case 0: return launch_instance<T, D, ROPE, EMASK_NONE, false>(args, mq, mk, mv, st);
-    case 1: return launch_instance<T, D, ROPE, EMASK_NONE, true>(args, mq, mk, mv, st);
-    case 2: return launch_instance<T, D, ROPE, EMASK_CAUSAL, false>(args, mq, mk, mv, st);
-    case 3: return launch_instance<T, D, ROPE, EMASK_CAUSAL, true>(args, mq, mk, mv, st);
-    case 4: return launch_instance<T, D, ROPE, EMASK_WINDOW, false>(args, mq, mk, mv, st);
-    default: return launch_instance<T, D, ROPE, EMASK_WINDOW, true>(args, mq, mk, mv, st);
+    case 0: return launch_instance<T, D, ROPE, EMASK_NONE, false>(args, mq, mk, mv, mo, st);
+    case 1: return launch_instance<T, D, ROPE, EMASK_NONE, true>(args, mq, mk, mv, mo, st);
+    case 2: return launch_instance<T, D, ROPE, EMASK_CAUSAL, false>(args, mq, mk, mv, mo, st);
+    case 3: return launch_instance<T, D, ROPE, EMASK_CAUSAL, true>(args, mq, mk, mv, mo, st);
+    case 4: return launch_instance<T, D, ROPE, EMASK_WINDOW, false>(args, mq, mk, mv, mo, st);
+    default: return launch_instance<T, D, ROPE, EMASK_WINDOW, true>(args, mq, mk, mv, mo, st);
   }
 }
 
 // Entry points of the instantiation units: dtype is AF_F16 / AF_BF16.
-int launch_d64_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
-int launch_d64_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
-int launch_d128_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
-int launch_d128_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d64_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d64_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d128_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_d128_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 
 #define AF_DEFINE_TC_UNIT(NAME, DIM, ROPE_MODE)                                                              \
   int NAME(int dtype, const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, \
-           cudaStream_t st) {                                                                                \
-    if (dtype == AF_F16) return launch_composition<__half, DIM, ROPE_MODE>(args, mq, mk, mv, st);            \
-    return launch_composition<__nv_bfloat16, DIM, ROPE_MODE>(args, mq, mk, mv, st);                          \
+           const CUtensorMap& mo, cudaStream_t st) {                                                         \
+    if (dtype == AF_F16) return launch_composition<__half, DIM, ROPE_MODE>(args, mq, mk, mv, mo, st);        \
+    return launch_composition<__nv_bfloat16, DIM, ROPE_MODE>(args, mq, mk, mv, mo, st);                      \
   }
 
 }  // namespace tc

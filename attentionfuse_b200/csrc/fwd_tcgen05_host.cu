@@ -48,12 +48,14 @@ size_t map_hash(const MapKey& k) {
   return (size_t)((h >> 24) % kMapSlots);
 }
 
-int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows);
+int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows,
+               int box_cols);
 
-// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box 64 x box_rows x 1 x 1.
+// (B, H, N, D) tensor with element strides -> 4-D tiled map {D, N, H, B}, box box_cols x box_rows x 1 x 1
+// (box_cols * 2 bytes <= 128, the swizzle span).
 int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st,
-             int box_rows = 128) {
-  const MapKey key{ptr, st[0], st[1], st[2], dtype, B, H, N, D, box_rows};
+             int box_rows = 128, int box_cols = 64) {
+  const MapKey key{ptr, st[0], st[1], st[2], dtype, B, H, N, D, box_rows + (box_cols << 16)};
   const size_t slot = map_hash(key);
   {
     std::lock_guard<std::mutex> lock(g_map_mu);
@@ -62,7 +64,7 @@ int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, 
       return AF_OK;
     }
   }
-  const int rc = encode_map(out, dtype, ptr, B, H, N, D, st, box_rows);
+  const int rc = encode_map(out, dtype, ptr, B, H, N, D, st, box_rows, box_cols);
   if (rc != AF_OK) return rc;
   std::lock_guard<std::mutex> lock(g_map_mu);
   g_map_cache[slot].key = key;
@@ -71,7 +73,8 @@ int make_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, 
   return AF_OK;
 }
 
-int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows) {
+int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N, int D, const int64_t* st, int box_rows,
+               int box_cols) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(AF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t esz = 2;
@@ -82,7 +85,7 @@ int encode_map(CUtensorMap* out, int dtype, const void* ptr, int B, int H, int N
   if (H == 1) sH = sN * (cuuint64_t)N;
   if (B == 1) sB = sH * (cuuint64_t)H;
   cuuint64_t strides[3] = {sN, sH, sB};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(out, dtype == AF_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -301,17 +304,19 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
     k_stride[3] = 1; k_stride[2] = p.D; k_stride[1] = (int64_t)p.N_kv * p.D; k_stride[0] = k_stride[1] * p.H_kv;
   }
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int rc;
   if ((rc = make_map(&mq, p.dtype, q_ptr, p.B, p.H_q, p.N_q, p.D, q_stride)) != AF_OK) return rc;
   if ((rc = make_map(&mk, p.dtype, k_ptr, p.B, p.H_kv, p.N_kv, p.D, k_stride)) != AF_OK) return rc;
   if ((rc = make_map(&mv, p.dtype, p.v, p.B, p.H_kv, p.N_kv, p.D, p.v_stride)) != AF_OK) return rc;
+  // output rows leave through a TMA store: one box = the 32 rows of a warp x half of the head dim
+  if ((rc = make_map(&mo, p.dtype, a.o, p.B, p.H_q, p.N_q, p.D, a.o_stride, 32, p.D / 2)) != AF_OK) return rc;
   if (p.D == 64) {
-    if (mode == tc::ROPE_NONE) return tc::launch_d64_norope(p.dtype, args, mq, mk, mv, st);
-    return tc::launch_d64_fused(p.dtype, args, mq, mk, mv, st);
+    if (mode == tc::ROPE_NONE) return tc::launch_d64_norope(p.dtype, args, mq, mk, mv, mo, st);
+    return tc::launch_d64_fused(p.dtype, args, mq, mk, mv, mo, st);
   }
-  if (mode == tc::ROPE_NONE) return tc::launch_d128_norope(p.dtype, args, mq, mk, mv, st);
-  return tc::launch_d128_fused(p.dtype, args, mq, mk, mv, st);
+  if (mode == tc::ROPE_NONE) return tc::launch_d128_norope(p.dtype, args, mq, mk, mv, mo, st);
+  return tc::launch_d128_fused(p.dtype, args, mq, mk, mv, mo, st);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -367,8 +372,9 @@ int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st) {
   if ((rc = make_map(&mq, a.dtype, a.q, a.B, a.H_kv, group, a.D, qs)) != AF_OK) return rc;
   if ((rc = make_map(&mk, a.dtype, a.k, a.B, a.H_kv, a.N_kv, a.D, a.k_stride)) != AF_OK) return rc;
   if ((rc = make_map(&mv, a.dtype, a.v, a.B, a.H_kv, a.N_kv, a.D, a.v_stride)) != AF_OK) return rc;
-  if (a.D == 64) return tc::launch_d64_norope(a.dtype, args, mq, mk, mv, st);
-  return tc::launch_d128_norope(a.dtype, args, mq, mk, mv, st);
+  // the split-K epilogue writes fp32 partials with plain stores: the output map is not used
+  if (a.D == 64) return tc::launch_d64_norope(a.dtype, args, mq, mk, mv, mq, st);
+  return tc::launch_d128_norope(a.dtype, args, mq, mk, mv, mq, st);
 }
 
 }  // namespace af
