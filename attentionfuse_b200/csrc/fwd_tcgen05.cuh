@@ -96,6 +96,27 @@ struct Barriers {
   float xchg[SOFTMAX_THREADS];   // reference maximum / row sum exchange between the two halves of a row
 };
 
+// Division of a non-negative int by a divisor fixed per launch (round-up multiplier method): the
+// item decode runs once per item in every role and a hardware-emulated division costs about as
+// much as a tenth of a key tile.
+struct FastDiv {
+  uint32_t mul, shr;   // shr == 0: divisor 1
+  __host__ static FastDiv make(uint32_t d) {
+    FastDiv f{0u, 0u};
+    if (d <= 1) return f;
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;
+    f.mul = (uint32_t)(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+    f.shr = l;
+    return f;
+  }
+  __device__ __forceinline__ int div(int n) const {
+    if (shr == 0) return n;
+    const uint32_t q = __umulhi((uint32_t)n, mul);
+    return (int)(((((uint32_t)n - q) >> 1) + q) >> (shr - 1));
+  }
+};
+
 static_assert(sizeof(Barriers) <= 1536, "Cfg::SMEM_BYTES reserves 1536 bytes for the barriers and the exchange");
 
 struct TcArgs {
@@ -105,6 +126,7 @@ struct TcArgs {
   int q_tiles_per_block;    // block_m / 128
   int total_items;          // num_m_blocks * B * H_q query tiles (split mode: num_splits * B * H)
   int grid_ctas;            // CTAs to launch: one per SM (persistent) or one per item
+  FastDiv div_bh, div_hq, div_group;   // by B * H_q, by H_q, by H_q / H_kv
   // Split-K decode mode (num_splits > 0): the "query rows" of an item are the query heads of one
   // KV group (N_q = group size, one pseudo-head per KV head), the keys of a sequence are dealt out
   // to num_splits items, and the epilogue writes un-normalised partials (m, l, acc) for the
@@ -181,16 +203,17 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
   const int w = (int)w64;
   const AfProblem& p = args.a.p;
   const int bh_count = p.B * p.H_q;
-  const int bh = w % bh_count;
-  it.b = bh / p.H_q;
-  it.h = bh % p.H_q;
-  it.h_kv = it.h / (p.H_q / p.H_kv);
+  const int w_over_bh = args.div_bh.div(w);
+  const int bh = w - w_over_bh * bh_count;
+  it.b = args.div_hq.div(bh);
+  it.h = bh - it.b * p.H_q;
+  it.h_kv = args.div_group.div(it.h);
   it.split = 0;
   it.n_kv = p.N_kv;
   if (SPLIT) {
     // split-K decode: one query tile per (batch, pseudo-head); the 128-key tiles of the valid
     // length are dealt out evenly to the splits
-    it.split = w / bh_count;
+    it.split = w_over_bh;
     it.m0 = 0;
     TileWalk& wk = it.walk;
     wk.list = nullptr; wk.slots = nullptr; wk.per_block = 1; wk.step = 1;
@@ -200,7 +223,7 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
     wk.n_tiles = (int)((int64_t)(it.split + 1) * tiles / args.num_splits) - wk.first_tile;
     return true;
   }
-  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - w / bh_count) : (w / bh_count);
+  const int m_blk = (EMASK == EMASK_CAUSAL) ? (args.num_m_blocks - 1 - w_over_bh) : w_over_bh;
   it.m0 = m_blk * BM;
   it.walk = make_walk(p, args, m_blk, it.h);
   return true;
@@ -346,27 +369,66 @@ __device__ __forceinline__ float row_max(const uint32_t (&xr)[NC]) {
 //   EXP_AFFINE     y = x * scale2 + slope_c * c + shift     (ALiBi folded in, c = column index)
 //   EXP_PRESCALED  y = x + shift                            (scores already scaled and biased)
 enum { EXP_SCALE = 0, EXP_AFFINE = 1, EXP_PRESCALED = 2 };
+// Packed fp32 pairs (sm_100: fma / add on two fp32 values in one 64-bit register pair, one issue
+// slot): the scale-and-shift and the row sum of the exponent pass take half the instructions.
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <typename T, int KIND, int NC>
 __device__ __forceinline__ void exp_pass(const uint32_t (&xr)[NC], uint32_t (&pk)[NC / 2], float scale2, float shift,
                                          float slope_c, float& rsum) {
-  float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (KIND == EXP_AFFINE) {
+    float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < NC; c += 4) {
+      float e[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float x = __uint_as_float(xr[c + u]);
+        e[u] = ex2_approx(fmaf(x, scale2, fmaf(slope_c, (float)(c + u), shift)));
+        rs4[u] += e[u];
+      }
+      pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
+      pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
+    }
+    rsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+    return;
+  }
+  const uint64_t sc2 = f32x2_pack(scale2, scale2), sh2 = f32x2_pack(shift, shift);
+  uint64_t rs2[2] = {f32x2_pack(0.f, 0.f), f32x2_pack(0.f, 0.f)};
 #pragma unroll
   for (int c = 0; c < NC; c += 4) {
-    float e[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float x = __uint_as_float(xr[c + u]);
-      float y;
-      if (KIND == EXP_PRESCALED) y = x + shift;
-      else if (KIND == EXP_AFFINE) y = fmaf(x, scale2, fmaf(slope_c, (float)(c + u), shift));
-      else y = fmaf(x, scale2, shift);
-      e[u] = ex2_approx(y);
-      rs4[u] += e[u];
+    for (int u = 0; u < 2; ++u) {
+      const uint64_t x2 = f32x2_pack(__uint_as_float(xr[c + 2 * u]), __uint_as_float(xr[c + 2 * u + 1]));
+      const uint64_t y2 = (KIND == EXP_PRESCALED) ? f32x2_add(x2, sh2) : f32x2_fma(x2, sc2, sh2);
+      float y0, y1;
+      f32x2_unpack(y2, y0, y1);
+      const float e0 = ex2_approx(y0), e1 = ex2_approx(y1);
+      rs2[u] = f32x2_add(rs2[u], f32x2_pack(e0, e1));
+      pk[(c >> 1) + u] = Pack2<T>::run(e0, e1);
     }
-    pk[c >> 1] = Pack2<T>::run(e[0], e[1]);
-    pk[(c >> 1) + 1] = Pack2<T>::run(e[2], e[3]);
   }
-  rsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+  float a0, a1, b0, b1;
+  f32x2_unpack(rs2[0], a0, a1);
+  f32x2_unpack(rs2[1], b0, b1);
+  rsum = (a0 + a1) + (b0 + b1);
 }
 
 // One instantiation per composition: element type, head_dim, RoPE mode, element-level mask and
@@ -738,6 +800,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       // through the same words (two hand-shakes; the next item's words are written only after
       // this item's have been read).
       if (!alive) break;
+      if (!SPLIT && lane == 0) bulk_wait_read_all();   // previous item's staged rows: long gone by now
       float c0 = 0.f, c1 = 0.f, m_all = 0.f, l_sum = 0.f;
       if (half == 1) {
         bars->xchg[rtid] = m_ref;
@@ -804,8 +867,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         // drops the rows past N_q.  The staging region is the warp's own; before it is written
         // again the previous store must have read it.
         const uint32_t stage = sO + (uint32_t)((half * 4 + (warp & 3)) * 32 * 128);
-        if (lane == 0) bulk_wait_read_all();
-        __syncwarp();
+        __syncwarp();   // lane 0 has seen the previous store off (below, before the exchange)
 #pragma unroll
         for (int q8 = 0; q8 < D / 16; ++q8) {
           uint4 v;

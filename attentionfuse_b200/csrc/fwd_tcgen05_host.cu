@@ -277,6 +277,9 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   args.q_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_m / tc::BM : 1;
   AF_REQUIRE((int64_t)args.num_m_blocks * p.B * p.H_q <= 0x7fffffff, "too many tiles for one launch");
   args.total_items = args.num_m_blocks * p.B * p.H_q;
+  args.div_bh = tc::FastDiv::make((uint32_t)(p.B * p.H_q));
+  args.div_hq = tc::FastDiv::make((uint32_t)p.H_q);
+  args.div_group = tc::FastDiv::make((uint32_t)(p.H_q / p.H_kv));
   {
     // One CTA fits per SM (shared memory), so the kernel runs persistently: one CTA per SM walks
     // its share of the query tiles with the pipeline kept full across tile boundaries (measured
@@ -364,6 +367,9 @@ int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st) {
   args.ws_m = a.ws_m; args.ws_l = a.ws_l; args.ws_acc = a.ws_acc;
   AF_REQUIRE((int64_t)a.num_splits * a.B * a.H_kv <= 0x7fffffff, "too many items for one launch");
   args.total_items = a.num_splits * a.B * a.H_kv;
+  args.div_bh = tc::FastDiv::make((uint32_t)(p.B * p.H_q));
+  args.div_hq = tc::FastDiv::make((uint32_t)p.H_q);
+  args.div_group = tc::FastDiv::make(1u);   // one pseudo-head per KV head
   int sms = 0;
   { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
   args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
