@@ -324,11 +324,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // loads; whatever both wrote to shared memory before is visible afterwards.  The words alternate
 // between two slots by the parity of the count, so a warp that runs ahead to its next hand-shake
 // cannot overwrite a word its partner has not read yet.  The wait is bounded like the mbarrier
-// waits (a hardware named barrier would hang if the partner left after a time-out).
+// waits (a hardware named barrier would hang if the partner left after a time-out).  It orders
+// shared-memory traffic only: the two warps never touch each other's TMEM columns.
 __device__ __forceinline__ bool pair_sync(Barriers* bars, int warp, int lane, uint32_t& count,
                                           volatile int* abort_flag) {
   ++count;
-  tc_fence_before_sync();   // orders this thread's TMEM accesses against the partner's
   __syncwarp();
   uint32_t* mine = &bars->pair_flag[count & 1][warp];
   const uint32_t* theirs = &bars->pair_flag[count & 1][warp ^ 4];
@@ -348,7 +348,6 @@ __device__ __forceinline__ bool pair_sync(Barriers* bars, int warp, int lane, ui
     }
   }
   __syncwarp();
-  tc_fence_after_sync();
   return true;
 }
 
