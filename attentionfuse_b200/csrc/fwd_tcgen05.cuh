@@ -987,6 +987,7 @@ int launch_d64_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtens
 int launch_d64_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 int launch_d128_norope(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 int launch_d128_fused(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
+int launch_pair_d128(int dtype, const TcArgs&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, cudaStream_t);
 
 #define AF_DEFINE_TC_UNIT(NAME, DIM, ROPE_MODE)                                                              \
   int NAME(int dtype, const TcArgs& args, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, \

@@ -1,6 +1,7 @@
 // Host side of the tcgen05 forward: support predicate, TMA descriptor encoding, RoPE mode
 // selection (fused in shared memory vs. a one-off K pre-rotation into caller workspace) and
 // dispatch to the per-(head_dim, RoPE mode) instantiation units.
+#include <cstdlib>
 #include <mutex>
 
 #include "fwd_tcgen05.cuh"
@@ -265,6 +266,16 @@ bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_st
   return true;
 }
 
+// The two-heads-per-CTA schedule (fwd_pair_tcgen05.cuh): head dim 128, an even number of query
+// heads per KV head, element masks only, operands already rotated.  ATTNFUSE_FWD_PAIR=0 in the
+// environment (read at every call) keeps the one-head schedule, for comparisons between the two.
+static bool pair_schedule_applies(const AfProblem& p, int rope_mode) {
+  if (p.D != 128 || rope_mode != tc::ROPE_NONE || p.mask_kind == AF_MASK_BLOCKS) return false;
+  if (p.H_kv < 1 || p.H_q % p.H_kv != 0 || ((p.H_q / p.H_kv) & 1) != 0) return false;
+  const char* e = std::getenv("ATTNFUSE_FWD_PAIR");
+  return !(e != nullptr && e[0] == '0');
+}
+
 int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   const char* why = nullptr;
   if (!fwd_tcgen05_supports(a.p, a.o, a.o_stride, &why))
@@ -314,6 +325,18 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   if ((rc = make_map(&mv, p.dtype, p.v, p.B, p.H_kv, p.N_kv, p.D, p.v_stride)) != AF_OK) return rc;
   // output rows leave through a TMA store: one box = the 32 rows of a warp x half of the head dim
   if ((rc = make_map(&mo, p.dtype, a.o, p.B, p.H_q, p.N_q, p.D, a.o_stride, 32, p.D / 2)) != AF_OK) return rc;
+  if (pair_schedule_applies(p, mode)) {
+    // two query heads of a KV group per CTA: one K / V load feeds two S products
+    const int pairs = p.H_q / 2;
+    args.total_items = args.num_m_blocks * p.B * pairs;
+    args.div_bh = tc::FastDiv::make((uint32_t)(p.B * pairs));
+    args.div_hq = tc::FastDiv::make((uint32_t)pairs);
+    args.div_group = tc::FastDiv::make((uint32_t)(p.H_q / p.H_kv / 2));
+    int sms = 0;
+    { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
+    args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
+    return tc::launch_pair_d128(p.dtype, args, mq, mk, mv, mo, st);
+  }
   if (p.D == 64) {
     if (mode == tc::ROPE_NONE) return tc::launch_d64_norope(p.dtype, args, mq, mk, mv, mo, st);
     return tc::launch_d64_fused(p.dtype, args, mq, mk, mv, mo, st);

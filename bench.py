@@ -448,7 +448,7 @@ def main():
                      "frac": per_gpu / pk["bf16_tflops"], "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
                      "traffic_source": "scaled_from_capture (attention kernel, batch-2 ncu capture x 2)",
                      "peak_kind": f"{pk_kind} cuBLAS bf16 burst",
-                     "kernel": "rope_prepass_kernel<bf16,128> + fwd_tcgen05_kernel<bf16,D=128,causal> (one step = both launches)",
+                     "kernel": "rope_prepass_kernel<bf16,128> + fwd_pair_kernel<bf16,causal> (two query heads of a KV group per CTA; one step = both launches)",
                      "step_ms": ms_step, "frac_of_nominal_2250": per_gpu / 2250.0,
                      "attention_kernel_alone": {"ms": kernel_ms, "tflops": kernel_tflops,
                                                 "frac": kernel_tflops / pk["bf16_tflops"]}},

@@ -58,8 +58,13 @@ def test_chunk_matches_oracle_and_full_problem(variant, case):
     assert_close(got, want, dtype, what=f"chunk vs oracle {variant}")
     # size-independent property: the chunk is a slice of the square problem
     full = fn(Qfull.to(DEV), K.to(DEV), V.to(DEV), family=family, **kw)
-    tol = 1e-5 if dtype == torch.float32 else 4e-3
-    assert (got.float() - full[:, :, off:off + N_q].float()).abs().max().item() <= tol
+    # fp32 and the one-head tensor-core schedule walk a row in the same order in both problems;
+    # in the two-heads-per-CTA schedule a row's fast / classic softmax steps are voted by its warp,
+    # whose other rows differ between the two problems, so a result may land one ulp apart.
+    ref = full[:, :, off:off + N_q].float()
+    half_ulp = 2.0 ** (-7 if dtype == torch.bfloat16 else -10)
+    tol = 1e-5 if dtype == torch.float32 else max(4e-3, half_ulp * ref.abs().max().item())
+    assert (got.float() - ref).abs().max().item() <= tol
 
 
 def test_offsets_are_validated_and_cross_attention_rule_stays():

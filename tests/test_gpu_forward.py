@@ -245,6 +245,11 @@ def test_rope_prepass_and_in_kernel_rotation_agree(D, dtype, monkeypatch):
     cos, sin = orc.build_rope_cache(N, D, 500000.0, dtype)
     q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
     want = orc.attention(Q, K, V, causal=True, cos=cos, sin=sin)
+    # The bit-for-bit comparison is between the two rotation schedules of ONE attention schedule:
+    # at head dim 128 rotated operands of a GQA problem would otherwise take the two-heads-per-CTA
+    # kernel, which the in-kernel rotation does not have (same arithmetic per element, another
+    # order of the online-softmax steps).  That kernel is checked against the oracle below.
+    monkeypatch.setenv("ATTNFUSE_FWD_PAIR", "0")
     monkeypatch.setenv("ATTNFUSE_ROPE_IN_KERNEL", "0")
     pre = causal_rope(q, k, v, cos=cos.to(DEV), sin=sin.to(DEV))
     monkeypatch.setenv("ATTNFUSE_ROPE_IN_KERNEL", "1")
@@ -252,6 +257,10 @@ def test_rope_prepass_and_in_kernel_rotation_agree(D, dtype, monkeypatch):
     assert_close(pre, want, dtype, what="pre-pass")
     assert_close(fused, want, dtype, what="in-kernel")
     assert torch.equal(pre, fused)
+    monkeypatch.setenv("ATTNFUSE_FWD_PAIR", "1")
+    monkeypatch.setenv("ATTNFUSE_ROPE_IN_KERNEL", "0")
+    paired = causal_rope(q, k, v, cos=cos.to(DEV), sin=sin.to(DEV))
+    assert_close(paired, want, dtype, what="pre-pass, two heads per CTA")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -267,7 +276,12 @@ def test_row_maximum_jumps_in_late_tiles(variant, dtype):
     K = (K.float() * ramp).to(dtype)
     K[:, :, 650] = (K[:, :, 650].float() * 3).to(dtype)
     got, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05)
-    assert_close(got, want, dtype, what=f"late maxima {variant} {dtype}")
+    # These rows are one-hot: an output element is a single V element, up to |4| here, where one
+    # ulp of bf16 is 1.6e-2 -- the flat 2e-2 of the unit-scale cases is scaled with that magnitude.
+    scale = max(1.0, want.abs().max().item() / 2.0)
+    assert torch.isfinite(got).all()
+    ma, rf = orc.max_abs(got.cpu(), want), orc.rel_fro(got.cpu(), want)
+    assert ma <= 2e-2 * scale and rf <= 1e-2, f"late maxima {variant} {dtype}: max-abs {ma:.3e} (scale {scale:.2f}), rel-Frobenius {rf:.3e}"
 
 
 @pytest.mark.parametrize("variant", ["dense", "causal", "window", "causal_rope"])
@@ -278,3 +292,37 @@ def test_more_items_than_sms(variant):
     Q, K, V = qkv(1300, B, Hq, Hkv, N, N, D, torch.bfloat16)
     got, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05, window=200)
     assert_close(got, want, torch.bfloat16, what=f"persistent {variant}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("variant", ["dense", "causal", "window", "causal_alibi", "causal_rope"])
+def test_two_heads_per_cta_schedule(variant, dtype, monkeypatch):
+    """At head dim 128 a GQA problem with an even group runs two query heads of a KV group per CTA
+    (one K / V load, two S products, a softmax stream per head).  Same arithmetic per element as
+    the one-head schedule: both are checked against the oracle, and against each other within
+    the half-precision bound.  Several items per CTA, a ragged last tile, groups of 2 and 6."""
+    for (B, Hq, Hkv, N) in ((2, 4, 2, 130), (3, 24, 4, 1000), (1, 12, 2, 1333)):
+        Q, K, V = qkv(4100 + N, B, Hq, Hkv, N, N, 128, dtype)
+        monkeypatch.setenv("ATTNFUSE_FWD_PAIR", "1")
+        pair, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05, window=200, rope_base=500000.0)
+        monkeypatch.setenv("ATTNFUSE_FWD_PAIR", "0")
+        single, _ = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05, window=200, rope_base=500000.0)
+        assert_close(pair, want, dtype, what=f"two heads per CTA {variant} {Hq}/{Hkv} N{N}")
+        assert_close(single, want, dtype, what=f"one head per CTA {variant} {Hq}/{Hkv} N{N}")
+        assert_close(pair, single.cpu().float(), dtype, what=f"two heads vs one head per CTA {variant}")
+
+
+def test_two_heads_per_cta_lse_and_offset():
+    """The LSE rows of the paired schedule and a chunk of queries against a longer cache."""
+    B, Hq, Hkv, N, D = 2, 8, 2, 700, 128
+    Q, K, V = qkv(4300, B, Hq, Hkv, N, N, D, torch.bfloat16)
+    L = torch.empty(B, Hq, N, dtype=torch.float32, device=DEV)
+    graph = causal(Q.to(DEV), K.to(DEV), V.to(DEV), return_graph=True)
+    out = run_attention(graph, Q.to(DEV), K.to(DEV), V.to(DEV), save_lse=L, family=_lib.AF_FAMILY_TCGEN05)
+    want, want_l = orc.attention(Q, K, V, causal=True, return_lse=True)
+    assert_close(out, want, torch.bfloat16, what="paired causal")
+    assert (L.cpu() - want_l).abs().max().item() < 2e-2
+    off, nq = 400, 250
+    Qc = Q[:, :, off:off + nq].contiguous()
+    got = causal(Qc.to(DEV), K.to(DEV), V.to(DEV), q_offset=off, family=_lib.AF_FAMILY_TCGEN05)
+    assert_close(got, orc.attention(Qc, K, V, causal=True, q_offset=off), torch.bfloat16, what="paired chunk")
