@@ -390,11 +390,12 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(o_tmem + cc * 32, &o[cc * 32]);
         tmem_wait_ld();
         tc_fence_before_sync();
+        mbar_arrive(&bars->o_free[q]);   // the next item's first P.V product may overwrite O_q
       } else {
+        // no key tile in reach of these rows: zeros, and no hand-over (the MMA threads skip the item)
 #pragma unroll
         for (int i = 0; i < D; ++i) o[i] = 0u;
       }
-      mbar_arrive(&bars->o_free[q]);   // the next item's first P.V product may overwrite O_q
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {
         if (lane == 0) bulk_wait_read_all();   // the region's previous store has read it

@@ -100,3 +100,21 @@ def test_single_query_step_with_masks_and_rotation(variant):
     want = orc.attention(Q1, K, V, q_offset=off, **oracle_kwargs(variant, Hq, dtype, window, cos, sin))
     assert got.shape == (B, Hq, 1, D)
     assert_close(got, want, dtype, what=f"single-row step {variant}")
+
+
+@pytest.mark.parametrize("case", [(torch.bfloat16, 2, 4, 2, 128), (torch.float16, 1, 4, 4, 64), (torch.bfloat16, 1, 6, 2, 128)],
+                         ids=["bf16-d128-pairs", "f16-d64", "bf16-d128-odd-group"])
+def test_window_rows_out_of_reach_of_every_key(case):
+    """Queries placed past the cache by more than the window see no key at all: whole query tiles
+    without a key tile (the persistent kernels skip them in the MMA roles and write zero rows),
+    next to tiles that are partly and fully in reach.  Several (batch, head) items per CTA so that
+    the barrier phases run across such items."""
+    dtype, B, Hq, Hkv, D = case
+    N_kv, N_q, off, window = 300, 384, 200, 64
+    Q, K, V = qkv(5200, B, Hq, Hkv, N_q, N_kv, D, dtype)
+    fn = graphs(Hq, window)["window"]
+    got = fn(Q.to(DEV), K.to(DEV), V.to(DEV), q_offset=off, family=_lib.AF_FAMILY_TCGEN05)
+    want = orc.attention(Q, K, V, q_offset=off, window=window)
+    assert_close(got, want, dtype, what="window past the cache")
+    last = got[:, :, N_kv + window - off:].float()
+    assert last.numel() > 0 and (last == 0).all()
