@@ -88,7 +88,7 @@ struct Barriers {
   uint64_t q_full, q_ready, q_empty;
   uint64_t k_full[4], k_ready[4], k_empty[4];
   uint64_t v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2][2], pv_done[2];   // p_full[S buffer][half]
+  uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];   // [S buffer][half of the key columns]; head dim 128 uses [.][0] of s_full / pv_done
   uint64_t o_free;
   uint32_t tmem_base;
   int abort_flag;
@@ -442,7 +442,13 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
   constexpr int STAGES = C::STAGES, STAGES_V = C::STAGES_V;
   constexpr bool ROT_K = (ROPE == ROPE_FUSED);
   constexpr int AB_FMT = (Elem<T>::code == AF_BF16) ? 1 : 0;
-  constexpr uint32_t IDESC_QK = umma_idesc_f16(AB_FMT, BM, BN, 0, 0);
+  // Head dim 64: one S product per half of the key columns, each with barriers of its own, so the
+  // two softmax streams of a row never wait for each other (the operands are small enough that
+  // reading Q twice per tile does not load the shared-memory port; at head dim 128 it does, and
+  // the whole-tile product is faster there).
+  constexpr bool SPLIT_S = (D == 64);
+  constexpr int S_PARTS = SPLIT_S ? 2 : 1;
+  constexpr uint32_t IDESC_QK = umma_idesc_f16(AB_FMT, BM, SPLIT_S ? HALF_COLS : BN, 0, 0);
   constexpr uint32_t IDESC_PV = umma_idesc_f16(AB_FMT, BM, D, 0, 1);
 
   const AfFwdParams& a = args.a;
@@ -478,10 +484,11 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       mbar_init(&bars->v_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t][0], SOFTMAX_THREADS / 2);
-      mbar_init(&bars->p_full[t][1], SOFTMAX_THREADS / 2);
-      mbar_init(&bars->pv_done[t], 1);
+      for (int hh = 0; hh < 2; ++hh) {
+        mbar_init(&bars->s_full[t][hh], 1);
+        mbar_init(&bars->p_full[t][hh], SOFTMAX_THREADS / 2);
+        mbar_init(&bars->pv_done[t][hh], 1);
+      }
     }
     bars->abort_flag = 0;
     for (int i = 0; i < 16; ++i) (&bars->pair_flag[0][0])[i] = 0u;
@@ -575,20 +582,24 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           const int gg = g + j;                       // the CTA's running key-tile count
           const int s = gg % STAGES, t = gg & 1;
           if (!mbar_wait(ROT_K ? &bars->k_ready[s] : &bars->k_full[s], (gg / STAGES) & 1, abort_flag)) { ok = false; break; }
-          // S buffer t still holds P of tile gg-2 until its P.V product has run
-          if (gg >= 2 && !mbar_wait(&bars->pv_done[t], ((gg >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0);
-          // Descriptors are built once; a k-step or a ring stage only moves the start-address
-          // field (address >> 4), so the issuing thread spends one add per operand.
+          // Descriptors are built once; a k-step, a ring stage or a half only moves the
+          // start-address field (address >> 4), so the issuing thread spends one add per operand.
           const uint64_t kdesc = desc_k0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
+          for (int hh = 0; hh < S_PARTS && ok; ++hh) {
+            // S buffer t (the half's columns of it) still holds P of tile gg-2 until its P.V product has run
+            if (gg >= 2 && !mbar_wait(&bars->pv_done[t][hh], ((gg >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t d_tmem = tmem + (t ? C::COL_S1 : C::COL_S0) + hh * HALF_COLS;
+            const uint64_t kh = kdesc + (uint64_t)((hh * HALF_COLS * 128) >> 4);   // keys 64 hh .. : rows of the K tile
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
-            umma_ss(d_tmem, desc_q0 + off, kdesc + off, IDESC_QK, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
+              umma_ss(d_tmem, desc_q0 + off, kh + off, IDESC_QK, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->s_full[t][hh]);
           }
+          if (!ok) break;
           umma_commit(&bars->k_empty[s]);
-          umma_commit(&bars->s_full[t]);
           // the item's last S product: the Q buffer may be refilled when it has run
           if (j + 1 == n_tiles) umma_commit(&bars->q_empty);
         }
@@ -628,10 +639,11 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
               umma_ts(o_tmem, p_tmem + kk * 8, vdesc + (uint64_t)(((hh * 4 + kk) * 2048) >> 4), IDESC_PV,
                       (j > 0 || kk > 0) ? 1u : 0u);
             }
+            if (SPLIT_S) umma_commit(&bars->pv_done[t][hh]);
           }
           if (!ok) break;
           umma_commit(&bars->v_empty[s]);
-          umma_commit(&bars->pv_done[t]);
+          if (!SPLIT_S) umma_commit(&bars->pv_done[t][0]);
         }
         g += n_tiles;
         ++qi;
@@ -673,7 +685,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         const int gg = g + j;                       // the CTA's running key-tile count
         const int t = gg & 1;
         const int key0 = walk.key0(j);
-        if (!mbar_wait(&bars->s_full[t], (gg >> 1) & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->s_full[t][SPLIT_S ? half : 0], (gg >> 1) & 1, abort_flag)) { alive = false; break; }
         tc_fence_after_sync();
         const uint32_t s_tmem = tmem + lane_base + (t ? C::COL_S1 : C::COL_S0);
         const uint32_t o_tmem = tmem + lane_base + (half ? C::COL_O1 : C::COL_O0);
@@ -754,7 +766,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           if (j > 0 && __any_sync(0xffffffffu, bump)) {
             // The accumulator is expressed relative to the old reference: rescale it in TMEM once
             // the previous P.V product has landed.
-            if (!mbar_wait(&bars->pv_done[(gg - 1) & 1], ((gg - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(&bars->pv_done[(gg - 1) & 1][SPLIT_S ? half : 0], ((gg - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
             tc_fence_after_sync();
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -826,7 +838,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       }
       if (n_tiles > 0) {
         const int gl = g + n_tiles - 1;
-        if (!mbar_wait(&bars->pv_done[gl & 1], (gl >> 1) & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->pv_done[gl & 1][0], (gl >> 1) & 1, abort_flag) ||
+            (SPLIT_S && !mbar_wait(&bars->pv_done[gl & 1][1], (gl >> 1) & 1, abort_flag))) { alive = false; break; }
         tc_fence_after_sync();
       }
       float o[D / 2];
