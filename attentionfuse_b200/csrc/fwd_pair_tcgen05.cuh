@@ -15,9 +15,10 @@
 // to the MMA thread on its own, so the P.V product of the first chunk runs under the exponent
 // pass of the second.
 //
-// Roles (352 threads): warps 0-3 softmax of slot 0, warps 4-7 softmax of slot 1, warp 8 TMA
-// producer (Q of both heads per item, K ring and V ring of two stages each), one thread of warp 9
-// issues S_q = Q_q K^T, one thread of warp 10 issues O_q += P_q V.  Every wait is bounded.
+// Roles (384 threads): warps 0-3 softmax of slot 0, warps 4-7 softmax of slot 1, warp 8 TMA
+// producer (Q of both heads per item, K ring and V ring of two stages each), one thread each of
+// warps 9 and 11 issues S_0 / S_1 = Q_q K^T, one thread of warp 10 issues O_q += P_q V.  Every
+// wait is bounded.
 #pragma once
 #include "fwd_tcgen05.cuh"
 
@@ -82,7 +83,7 @@ __device__ __forceinline__ bool pair_cursor_next(const TcArgs& args, TileCursor&
 }
 
 template <typename T, int EMASK, bool ALIBI>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(384, 1)
 fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                 const __grid_constant__ CUtensorMap tmap_o) {
@@ -109,10 +110,10 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
 
   if (tid == 0) {
     mbar_init(&bars->q_full, 1);
-    mbar_init(&bars->q_empty, 1);
+    mbar_init(&bars->q_empty, 2);      // one S-issuing thread per slot
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->k_empty[s], 2);
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
     }
@@ -197,10 +198,14 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         more_v = pair_cursor_next<EMASK>(args, cv);
       }
     }
-  } else if (warp == WARP_QK) {
-    // ============================== MMA issuer 1: S_q = Q_q K^T ==============================
+  } else if (warp == WARP_QK || warp == WARP_ROTATE) {
+    // ============================== MMA issuers 1a / 1b: S_q = Q_q K^T ==============================
+    // One issuing thread per slot, in warps of different schedulers: the issuing threads take
+    // issue slots from the softmax warps they share a scheduler with, and the slowest of a slot's
+    // four softmax warps sets the slot's pace.
     if (lane == 0) {
-      const uint64_t desc_q0 = umma_desc_sw128(sQ, 16, 1024);
+      const int q = (warp == WARP_QK) ? 0 : 1;
+      const uint64_t qdesc = umma_desc_sw128(sQ + q * C::TILE_BYTES, 16, 1024);
       const uint64_t desc_k0 = umma_desc_sw128(sK0, 16, 1024);
       TileCursor cu;
       cursor_init(cu);
@@ -210,27 +215,24 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         if (cu.j == 0 && !mbar_wait(&bars->q_full, cu.qi & 1, abort_flag)) break;
         if (!mbar_wait(&bars->k_full[s], (gg >> 1) & 1, abort_flag)) break;
         const uint64_t kdesc = desc_k0 + (uint64_t)((s * C::TILE_BYTES) >> 4);
-        for (int q = 0; q < 2 && ok; ++q) {
-          const uint64_t qdesc = desc_q0 + (uint64_t)((q * C::TILE_BYTES) >> 4);
-          for (int c = 0; c < 2 && ok; ++c) {
-            // One product per chunk of 64 key columns (rows 64 c .. 64 c + 63 of the K tile): the
-            // chunk's S columns hold P of the previous tile's chunk until its P.V product has run,
-            // so the first chunk of the next tile is under way while the softmax group is still
-            // in the second chunk of this one.
-            if (gg >= 1 && !mbar_wait(&bars->pv_done[q][c], (gg - 1) & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after_sync();
-            const uint32_t d_tmem = tmem + C::col_s(q) + c * 64;
-            const uint64_t kh = kdesc + (uint64_t)((c * 64 * 128) >> 4);
+        for (int c = 0; c < 2 && ok; ++c) {
+          // One product per chunk of 64 key columns (rows 64 c .. 64 c + 63 of the K tile): the
+          // chunk's S columns hold P of the previous tile's chunk until its P.V product has run,
+          // so the first chunk of the next tile is under way while the softmax group is still
+          // in the second chunk of this one.
+          if (gg >= 1 && !mbar_wait(&bars->pv_done[q][c], (gg - 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t d_tmem = tmem + C::col_s(q) + c * 64;
+          const uint64_t kh = kdesc + (uint64_t)((c * 64 * 128) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
-              umma_ss(d_tmem, qdesc + off, kh + off, IDESC_QK, kk > 0 ? 1u : 0u);
-            }
-            umma_commit(&bars->s_full[q][c]);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t off = (uint64_t)(((kk >> 2) * PANEL_BYTES + (kk & 3) * 32) >> 4);
+            umma_ss(d_tmem, qdesc + off, kh + off, IDESC_QK, kk > 0 ? 1u : 0u);
           }
+          umma_commit(&bars->s_full[q][c]);
         }
         if (!ok) break;
-        umma_commit(&bars->k_empty[s]);
+        umma_commit(&bars->k_empty[s]);        // both slots' products have to be through before the stage is refilled
         if (cu.j + 1 == cu.it.walk.n_tiles) umma_commit(&bars->q_empty);
       }
     }
@@ -445,7 +447,7 @@ int launch_pair_instance(const TcArgs& args, const CUtensorMap& mq, const CUtens
     AF_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  kern<<<(unsigned)args.grid_ctas, 352, smem, st>>>(args, mq, mk, mv, mo);
+  kern<<<(unsigned)args.grid_ctas, 384, smem, st>>>(args, mq, mk, mv, mo);
   count_launch();
   return check_cuda(cudaGetLastError(), "fwd_pair launch");
 }
