@@ -680,6 +680,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       }
       const float slope2 = ALIBI ? load_slope<T>(p.slopes, h) * kLog2e : 0.f;
       float m_ref = -INFINITY, l_part = 0.f;        // m_ref in log2 units of the scaled score
+      bool ref_ok = false;   // warp-uniform: every row of the warp has a finite reference (it never becomes -inf again)
 
       for (int j = 0; j < n_tiles; ++j) {
         const int gg = g + j;                       // the CTA's running key-tile count
@@ -744,7 +745,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         // first, reference update, accumulator rescale, then P.
         float alpha = 1.f, rsum = 0.f;
         uint32_t pk[HALF_COLS / 2];
-        bool fast = j > 0 && affine && __all_sync(0xffffffffu, m_ref != -INFINITY);
+        bool fast = ref_ok && affine;
         if (fast) {
           exp_pass<T, ALIBI ? EXP_AFFINE : EXP_SCALE>(xr, pk, scale2, bias0 - m_ref, slope_c, rsum);
           fast = __all_sync(0xffffffffu, rsum <= kRowSumBound);
@@ -762,6 +763,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           const float m_next = bump ? mx : m_ref;
           alpha = bump ? ex2_approx(m_ref - m_next) : 1.f;
           m_ref = m_next;
+          ref_ok = __all_sync(0xffffffffu, m_ref != -INFINITY);
           const float neg_m = (m_next == -INFINITY) ? 0.f : -m_next;
           if (j > 0 && __any_sync(0xffffffffu, bump)) {
             // The accumulator is expressed relative to the old reference: rescale it in TMEM once
