@@ -41,9 +41,9 @@ CFG4 = dict(B=4, H_q=32, H_kv=8, N=4096, D=128, rope_base=500000.0)
 DECODE = dict(B=16, H_q=32, H_kv=8, L=32768, D=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload:
-# not measured by this run but scaled from an ncu capture of the same shape at batch 2 (133.6 MB;
+# not measured by this run but scaled from an ncu capture of the same shape at batch 2 (133.3 MB;
 # traffic grows in proportion to the batch), and labelled so in the JSON line.
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = 267.2e6
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = 266.7e6
 
 
 def peaks():
