@@ -184,18 +184,18 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
       };
       bool more_k = pair_cursor_next<EMASK>(args, ck);
       bool more_v = pair_cursor_next<EMASK>(args, cv);
-      bool ok = true;
-      if (more_k) {
-        ok = load_k();
-        more_k = ok && pair_cursor_next<EMASK>(args, ck);
-      }
-      while (ok && more_v) {
-        if (more_k) {
+      // K runs one tile ahead of V (a wait for a V slot never holds up a K load) -- except across
+      // an item boundary: the first K load of an item starts with a wait for the Q buffers (the
+      // previous item's last S product), so every V tile of the previous item goes out before it.
+      while (more_k || more_v) {
+        const bool at_boundary = more_k && ck.j == 0 && ck.qi > 0 && more_v && cv.gg < ck.gg;
+        if (more_k && !at_boundary && (!more_v || ck.gg <= cv.gg + 1)) {
           if (!load_k()) break;
           more_k = pair_cursor_next<EMASK>(args, ck);
+        } else {
+          if (!load_v()) break;
+          more_v = pair_cursor_next<EMASK>(args, cv);
         }
-        if (!load_v()) break;
-        more_v = pair_cursor_next<EMASK>(args, cv);
       }
     }
   } else if (warp == WARP_QK || warp == WARP_ROTATE) {
@@ -276,10 +276,11 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t s_tmem = tmem + lane_base + C::col_s(q);
     const uint32_t o_tmem = tmem + lane_base + C::col_o(q);
     const float scale2 = p.sm_scale * kLog2e;     // > 0 (checked on the host)
-    Item it;
+    Item it, it_next;
     int g = 0;
     bool alive = true;
-    for (int round = 0; alive && get_pair_item<EMASK>(args, round, it); ++round) {
+    bool have = get_pair_item<EMASK>(args, 0, it);
+    for (int round = 0; alive && have; ++round) {
       const TileWalk& walk = it.walk;
       const int n_tiles = walk.n_tiles;
       const int m0 = it.m0, b = it.b, h = it.h + q;
@@ -379,6 +380,8 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
       // Epilogue: O = O_q / l, L = m + log(l); the rows leave through shared memory and a TMA
       // store, 64 columns at a time (the warp's staging region holds 32 rows x 128 bytes).
       if (!alive) break;
+      // the next item is decoded here, under the wait for the last P.V product
+      const bool have_next = get_pair_item<EMASK>(args, round + 1, it_next);
       if (n_tiles > 0) {
         const int gl = g + n_tiles - 1;
         if (!mbar_wait(&bars->pv_done[q][1], gl & 1, abort_flag)) { alive = false; break; }
@@ -425,6 +428,8 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         a.lse[(int64_t)b * a.lse_stride[0] + (int64_t)h * a.lse_stride[1] + (int64_t)row * a.lse_stride[2]] =
             m_ref * kLn2 + logf(safe_l);
       g += n_tiles;
+      it = it_next;
+      have = have_next;
     }
     if (lane == 0) bulk_wait_all();   // the staged rows must have left shared memory before the CTA exits
   }

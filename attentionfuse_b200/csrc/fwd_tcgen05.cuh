@@ -549,18 +549,18 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       };
       bool more_k = cursor_next<EMASK, SPLIT>(args, ck);
       bool more_v = cursor_next<EMASK, SPLIT>(args, cv);
-      bool ok = true;
-      if (more_k) {
-        ok = load_k();
-        more_k = ok && cursor_next<EMASK, SPLIT>(args, ck);
-      }
-      while (ok && more_v) {
-        if (more_k) {
+      // K runs one tile ahead of V (a wait for a V slot never holds up a K load) -- except across
+      // an item boundary: the first K load of an item starts with a wait for the Q buffers (the
+      // previous item's last S product), so every V tile of the previous item goes out before it.
+      while (more_k || more_v) {
+        const bool at_boundary = more_k && ck.j == 0 && ck.qi > 0 && more_v && cv.gg < ck.gg;
+        if (more_k && !at_boundary && (!more_v || ck.gg <= cv.gg + 1)) {
           if (!load_k()) break;
           more_k = cursor_next<EMASK, SPLIT>(args, ck);
+        } else {
+          if (!load_v()) break;
+          more_v = cursor_next<EMASK, SPLIT>(args, cv);
         }
-        if (!load_v()) break;
-        more_v = cursor_next<EMASK, SPLIT>(args, cv);
       }
     }
   } else if (warp == WARP_QK) {
