@@ -291,7 +291,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip fwd+bwd / decode side measurements")
     ap.add_argument("--sweep", choices=["cfg2", "cfg3", "cfg5"],
                     help="time the other configurations of the baseline (one JSON line per case) instead of the bench line")
-    ap.add_argument("--profile-case", choices=["fwd", "bwd", "decode"],
+    ap.add_argument("--profile-case", choices=["fwd", "bwd", "decode", "fwd_d64"],
                     help="run three iterations of a small case of one kernel family and exit (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:
@@ -752,7 +752,8 @@ def sweep(which: str):
 def profile_case(which: str):
     """Small cases for profiler captures: tensors larger than L2 but only a few hundred MB on the
     device, three iterations, no timing.  fwd/bwd: the headline shape at batch 2; decode: B8 H32/8
-    D128 L16384 with per-sequence lengths."""
+    D128 L16384 with per-sequence lengths; fwd_d64: the GPT-2 / BERT geometry of the forward sweep
+    (12 heads of 64), causal, at batch 8 and N = 8192 so that the tensors (302 MB) exceed the L2."""
     import attentionfuse_b200 as af
     from attentionfuse_b200.runtime.flash_decode import run_flash_decode
     from oracle import attention_oracle as orc
@@ -763,7 +764,18 @@ def profile_case(which: str):
     def causal_rope(Q, K, V):
         return af.softmax(af.causal(af.rope(Q, K))) @ V
 
-    if which in ("fwd", "bwd"):
+    if which == "fwd_d64":
+        @af.attention
+        def causal(Q, K, V):
+            return af.softmax(af.causal(af.scaled_dot_product(Q, K))) @ V
+        B, H, N, D = 8, 12, 8192, 64
+        Q = torch.randn(B, H, N, D, generator=g, device=dev, dtype=dt)
+        K = torch.randn(B, H, N, D, generator=g, device=dev, dtype=dt)
+        V = torch.randn(B, H, N, D, generator=g, device=dev, dtype=dt)
+        with torch.no_grad():
+            for _ in range(3):
+                causal(Q, K, V)
+    elif which in ("fwd", "bwd"):
         B, Hq, Hkv, N, D = 2, CFG4["H_q"], CFG4["H_kv"], CFG4["N"], CFG4["D"]
         grad = which == "bwd"
         Q = torch.randn(B, Hq, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
