@@ -48,8 +48,8 @@ struct PairBarriers {
 };
 static_assert(sizeof(PairBarriers) <= 512, "PairCfg::SMEM_BYTES reserves 512 bytes for the barriers");
 
-// Item w of the pair schedule: heaviest first like get_item; args.div_bh / div_hq / div_group
-// divide by B * H_q / 2, H_q / 2 and (H_q / H_kv) / 2, and it.h is the first head of the pair.
+// Item w of the pair schedule: the order of get_item with head pairs as units; args.div_hq /
+// div_group divide by H_q / 2 and (H_q / H_kv) / 2, and it.h is the first head of the pair.
 template <int EMASK>
 __device__ __forceinline__ bool get_pair_item(const TcArgs& args, int round, Item& it) {
   const int G = (int)gridDim.x, c = (int)blockIdx.x;
@@ -58,8 +58,8 @@ __device__ __forceinline__ bool get_pair_item(const TcArgs& args, int round, Ite
   const int w = (int)w64;
   const AfProblem& p = args.a.p;
   const int pairs = p.H_q >> 1;
-  const int w_over_bp = args.div_bh.div(w);
-  const int bp = w - w_over_bp * (p.B * pairs);
+  int w_over_bp, bp;
+  split_item(args, w, args.num_m_blocks, w_over_bp, bp);
   it.b = args.div_hq.div(bp);
   const int pr = bp - it.b * pairs;
   it.h = pr * 2;

@@ -126,7 +126,16 @@ struct TcArgs {
   int q_tiles_per_block;    // block_m / 128
   int total_items;          // num_m_blocks * B * H_q query tiles (split mode: num_splits * B * H)
   int grid_ctas;            // CTAs to launch: one per SM (persistent) or one per item
-  FastDiv div_bh, div_hq, div_group;   // by B * H_q, by H_q, by H_q / H_kv
+  FastDiv div_hq, div_group;           // by H_q, by H_q / H_kv
+  // Item order.  The units -- (batch, head) pairs, heads of a KV group adjacent -- are taken in
+  // chunks whose K and V fit the L2 together; inside a chunk the items run row of query tiles by
+  // row (all units of the chunk, then the next row), so a key tile fetched from DRAM is still in
+  // the L2 when the chunk's other query tiles ask for it.  One chunk = all units is the plain
+  // row-major order.  Odd chunks run their rows in reverse, so that the item weights of a causal
+  // problem fall and rise continuously across chunk boundaries (the zig-zag deal evens out
+  // monotonic stretches, not steps).
+  int unit_chunk, items_per_chunk;     // units per chunk (divides the unit count); rows * unit_chunk
+  FastDiv div_ipc, div_chunk;          // by items_per_chunk, by unit_chunk
   // Split-K decode mode (num_splits > 0): the "query rows" of an item are the query heads of one
   // KV group (N_q = group size, one pseudo-head per KV head), the keys of a sequence are dealt out
   // to num_splits items, and the epilogue writes un-normalised partials (m, l, acc) for the
@@ -184,6 +193,15 @@ __device__ __forceinline__ TileWalk make_walk(const AfProblem& p, const TcArgs& 
   return w;
 }
 
+// Item number -> (row index in visiting order, unit); see TcArgs::unit_chunk.
+__device__ __forceinline__ void split_item(const TcArgs& args, int w, int n_rows, int& row_idx, int& unit) {
+  const int c = args.div_ipc.div(w);
+  const int r = w - c * args.items_per_chunk;
+  row_idx = args.div_chunk.div(r);
+  unit = c * args.unit_chunk + (r - row_idx * args.unit_chunk);
+  if (c & 1) row_idx = n_rows - 1 - row_idx;
+}
+
 // One work item = one 128-row query tile of one (batch, query head).
 struct Item {
   int m0, b, h, h_kv;
@@ -202,9 +220,8 @@ __device__ __forceinline__ bool get_item(const TcArgs& args, int round, Item& it
   if (w64 >= args.total_items) return false;
   const int w = (int)w64;
   const AfProblem& p = args.a.p;
-  const int bh_count = p.B * p.H_q;
-  const int w_over_bh = args.div_bh.div(w);
-  const int bh = w - w_over_bh * bh_count;
+  int w_over_bh, bh;   // row of query tiles in visiting order (split mode: the split), (batch, head) unit
+  split_item(args, w, SPLIT ? args.num_splits : args.num_m_blocks, w_over_bh, bh);
   it.b = args.div_hq.div(bh);
   it.h = bh - it.b * p.H_q;
   it.h_kv = args.div_group.div(it.h);

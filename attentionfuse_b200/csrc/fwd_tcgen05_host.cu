@@ -266,6 +266,39 @@ bool fwd_tcgen05_supports(const AfProblem& p, const void* o, const int64_t* o_st
   return true;
 }
 
+// Units per chunk of the item order (TcArgs::unit_chunk).  While all K and V of the problem fit the
+// 126 MB L2 with room to spare (96 MB: measured up to 67 MB, no re-reads from DRAM) the order is the
+// plain one, whose item weights the zig-zag deal balances to 0.3 %.  Beyond that every key tile is
+// fetched from DRAM many times over (11 x at 201 MB), and the units are taken in chunks: the largest
+// divisor of the unit count that is a multiple of `group_units` (the units of a KV group stay
+// together) and whose K and V stay inside 24 MB (a line used by SMs of both dies is held by both
+// halves of the L2, and Q and O stream through it as well; 24 against 40 MB measured).  Chunking
+// costs 2 - 4 % of balance in the static deal and gains 4 - 13 % at 134 - 268 MB of K and V.
+// ATTNFUSE_L2_KV_MB overrides the chunk budget and applies it at any size.
+static int choose_unit_chunk(int units, int group_units, double kv_bytes_per_unit) {
+  double budget = 24.0 * 1048576.0;
+  bool forced = false;
+  if (const char* e = std::getenv("ATTNFUSE_L2_KV_MB")) {
+    const double v = std::atof(e);
+    if (v > 0.0) { budget = v * 1048576.0; forced = true; }
+  }
+  if (group_units < 1) group_units = 1;
+  const double total = (double)units * kv_bytes_per_unit;
+  if (total <= budget || (!forced && total <= 96.0 * 1048576.0)) return units;
+  int best = group_units;
+  for (int d = group_units; d <= units; d += group_units)
+    if (units % d == 0 && (double)d * kv_bytes_per_unit <= budget) best = d;
+  return best;
+}
+
+static void set_item_order(tc::TcArgs& args, int units, int unit_chunk, int rows) {
+  args.unit_chunk = unit_chunk;
+  args.items_per_chunk = rows * unit_chunk;
+  args.div_ipc = tc::FastDiv::make((uint32_t)args.items_per_chunk);
+  args.div_chunk = tc::FastDiv::make((uint32_t)unit_chunk);
+  (void)units;
+}
+
 // The two-heads-per-CTA schedule (fwd_pair_tcgen05.cuh): head dim 128, an even number of query
 // heads per KV head, element masks only, operands already rotated.  ATTNFUSE_FWD_PAIR=0 in the
 // environment (read at every call) keeps the one-head schedule, for comparisons between the two.
@@ -288,9 +321,13 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
   args.q_tiles_per_block = p.mask_kind == AF_MASK_BLOCKS ? p.block_m / tc::BM : 1;
   AF_REQUIRE((int64_t)args.num_m_blocks * p.B * p.H_q <= 0x7fffffff, "too many tiles for one launch");
   args.total_items = args.num_m_blocks * p.B * p.H_q;
-  args.div_bh = tc::FastDiv::make((uint32_t)(p.B * p.H_q));
   args.div_hq = tc::FastDiv::make((uint32_t)p.H_q);
   args.div_group = tc::FastDiv::make((uint32_t)(p.H_q / p.H_kv));
+  {
+    const int group = p.H_q / p.H_kv;
+    const double kv_bytes = 2.0 * 2.0 * (double)p.N_kv * p.D / group;   // K and V of a query head's share
+    set_item_order(args, p.B * p.H_q, choose_unit_chunk(p.B * p.H_q, group, kv_bytes), args.num_m_blocks);
+  }
   {
     // One CTA fits per SM (shared memory), so the kernel runs persistently: one CTA per SM walks
     // its share of the query tiles with the pipeline kept full across tile boundaries (measured
@@ -329,9 +366,13 @@ int launch_fwd_tcgen05(const AfFwdParams& a, cudaStream_t st) {
     // two query heads of a KV group per CTA: one K / V load feeds two S products
     const int pairs = p.H_q / 2;
     args.total_items = args.num_m_blocks * p.B * pairs;
-    args.div_bh = tc::FastDiv::make((uint32_t)(p.B * pairs));
     args.div_hq = tc::FastDiv::make((uint32_t)pairs);
     args.div_group = tc::FastDiv::make((uint32_t)(p.H_q / p.H_kv / 2));
+    {
+      const int group_pairs = p.H_q / p.H_kv / 2;
+      const double kv_bytes = 2.0 * 2.0 * (double)p.N_kv * p.D / group_pairs;
+      set_item_order(args, p.B * pairs, choose_unit_chunk(p.B * pairs, group_pairs, kv_bytes), args.num_m_blocks);
+    }
     int sms = 0;
     { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
     args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
@@ -390,9 +431,9 @@ int launch_decode_split_tc(const AfDecodeParams& a, cudaStream_t st) {
   args.ws_m = a.ws_m; args.ws_l = a.ws_l; args.ws_acc = a.ws_acc;
   AF_REQUIRE((int64_t)a.num_splits * a.B * a.H_kv <= 0x7fffffff, "too many items for one launch");
   args.total_items = a.num_splits * a.B * a.H_kv;
-  args.div_bh = tc::FastDiv::make((uint32_t)(p.B * p.H_q));
   args.div_hq = tc::FastDiv::make((uint32_t)p.H_q);
   args.div_group = tc::FastDiv::make(1u);   // one pseudo-head per KV head
+  set_item_order(args, p.B * p.H_q, p.B * p.H_q, a.num_splits);   // splits x (batch, pseudo-head), plain order
   int sms = 0;
   { const int rc_sm = tc_sm_count(&sms); if (rc_sm != AF_OK) return rc_sm; }
   args.grid_ctas = (sms > 0 && sms < args.total_items) ? sms : args.total_items;
