@@ -146,6 +146,7 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
       tma_prefetch_desc(&tmap_k);
       tma_prefetch_desc(&tmap_v);
       tma_prefetch_desc(&tmap_o);
+      const uint64_t keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
       TileCursor ck, cv;   // K runs one tile ahead of V
       cursor_init(ck);
       cursor_init(cv);
@@ -158,8 +159,8 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
           for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int pn = 0; pn < 2; ++pn)
-              tma_load_4d(smem + q * C::TILE_BYTES + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, ck.it.m0,
-                          ck.it.h + q, ck.it.b);
+              tma_load_4d_hint(smem + q * C::TILE_BYTES + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, ck.it.m0,
+                               ck.it.h + q, ck.it.b, stream);
         }
         const int s = ck.gg & 1;
         if (ck.gg >= 2 && !mbar_wait(&bars->k_empty[s], ((ck.gg >> 1) & 1) ^ 1, abort_flag)) return false;
@@ -168,7 +169,7 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         unsigned char* dk = smem + C::TILE_BYTES * (2 + s);
 #pragma unroll
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, ck.it.h_kv, ck.it.b);
+          tma_load_4d_hint(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, ck.it.h_kv, ck.it.b, keep);
         return true;
       };
       auto load_v = [&]() -> bool {
@@ -179,7 +180,7 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         unsigned char* dv = smem + C::TILE_BYTES * (2 + C::STAGES + s);
 #pragma unroll
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, cv.it.h_kv, cv.it.b);
+          tma_load_4d_hint(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, cv.it.h_kv, cv.it.b, keep);
         return true;
       };
       bool more_k = pair_cursor_next<EMASK>(args, ck);
@@ -420,7 +421,7 @@ fwd_pair_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q,
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && row0 < p.N_q) {
-          tma_store_4d(&tmap_o, stage, c2 * 64, row0, h, b);
+          tma_store_4d_hint(&tmap_o, stage, c2 * 64, row0, h, b, l2_policy_evict_first());
           bulk_commit_group();
         }
       }

@@ -529,6 +529,8 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       tma_prefetch_desc(&tmap_o);
       // Two cursors over the same tile sequence: K runs one tile ahead of V, so that a wait for
       // a V slot (free only after the P.V product two tiles back) never holds up a K load.
+      // split-K decode reads every cache tile exactly once: nothing to keep there
+      const uint64_t stream = l2_policy_evict_first(), keep = SPLIT ? stream : l2_policy_evict_last();
       TileCursor ck, cv;
       cursor_init(ck);
       cursor_init(cv);
@@ -539,7 +541,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
           mbar_arrive_expect_tx(&bars->q_full, C::TILE_BYTES);
 #pragma unroll
           for (int pn = 0; pn < C::PANELS; ++pn)
-            tma_load_4d(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, ck.it.m0, ck.it.h, ck.it.b);
+            tma_load_4d_hint(smem + pn * PANEL_BYTES, &tmap_q, &bars->q_full, pn * 64, ck.it.m0, ck.it.h, ck.it.b, stream);
         }
         const int s = ck.gg % STAGES;
         const uint32_t par = ((ck.gg / STAGES) & 1) ^ 1;   // parity of the previous use of the slot
@@ -549,7 +551,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         const int key0 = ck.it.walk.key0(ck.j);
 #pragma unroll
         for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, ck.it.h_kv, ck.it.b);
+          tma_load_4d_hint(dk + pn * PANEL_BYTES, &tmap_k, &bars->k_full[s], pn * 64, key0, ck.it.h_kv, ck.it.b, keep);
         return true;
       };
       auto load_v = [&]() -> bool {
@@ -561,7 +563,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         const int key0 = cv.it.walk.key0(cv.j);
 #pragma unroll
         for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, cv.it.h_kv, cv.it.b);
+          tma_load_4d_hint(dv + pn * PANEL_BYTES, &tmap_v, &bars->v_full[s], pn * 64, key0, cv.it.h_kv, cv.it.b, keep);
         return true;
       };
       bool more_k = cursor_next<EMASK, SPLIT>(args, ck);
@@ -912,7 +914,7 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
         __syncwarp();
         const int row0 = m0 + (warp & 3) * 32;
         if (lane == 0 && row0 < p.N_q) {
-          tma_store_4d(&tmap_o, stage, half * (D / 2), row0, h, b);
+          tma_store_4d_hint(&tmap_o, stage, half * (D / 2), row0, h, b, l2_policy_evict_first());
           bulk_commit_group();
         }
         if (a.lse != nullptr && half == 0 && row < p.N_q)

@@ -751,7 +751,7 @@ def sweep(which: str):
 
 def profile_case(which: str):
     """Small cases for profiler captures: tensors larger than L2 but only a few hundred MB on the
-    device, three iterations, no timing.  fwd/bwd: the headline shape at batch 2; decode: B8 H32/8
+    device, three iterations, no timing.  fwd: the headline shape; bwd: the headline shape at batch 2; decode: B8 H32/8
     D128 L16384 with per-sequence lengths; fwd_d64: the GPT-2 / BERT geometry of the forward sweep
     (12 heads of 64), causal, at batch 8 and N = 8192 so that the tensors (302 MB) exceed the L2."""
     import attentionfuse_b200 as af
@@ -776,7 +776,8 @@ def profile_case(which: str):
             for _ in range(3):
                 causal(Q, K, V)
     elif which in ("fwd", "bwd"):
-        B, Hq, Hkv, N, D = 2, CFG4["H_q"], CFG4["H_kv"], CFG4["N"], CFG4["D"]
+        # forward: the bench's own batch (0.6 GB on the device with the rotation workspace); backward: batch 2
+        B, Hq, Hkv, N, D = (CFG4["B"] if which == "fwd" else 2), CFG4["H_q"], CFG4["H_kv"], CFG4["N"], CFG4["D"]
         grad = which == "bwd"
         Q = torch.randn(B, Hq, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
         K = torch.randn(B, Hkv, N, D, generator=g, device=dev, dtype=dt, requires_grad=grad)
