@@ -41,9 +41,10 @@ CFG4 = dict(B=4, H_q=32, H_kv=8, N=4096, D=128, rope_base=500000.0)
 DECODE = dict(B=16, H_q=32, H_kv=8, L=32768, D=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel on this workload:
-# not measured by this run but scaled from an ncu capture of the same shape at batch 2 (133.3 MB;
-# traffic grows in proportion to the batch), and labelled so in the JSON line.
-FWD_KERNEL_DRAM_TRAFFIC_BYTES = 266.7e6
+# not measured by this run but taken from the ncu capture of the same workload (batch 4: 266.7 MB
+# read + 81.8 MB written; profiles/fwd_tcgen05_causal_rope_bf16_d128.md), and labelled so in the
+# JSON line.
+FWD_KERNEL_DRAM_TRAFFIC_BYTES = 348.5e6
 
 
 def peaks():
@@ -446,7 +447,7 @@ def main():
         # the whole causal+RoPE step: rotation pre-pass + attention kernel, the two launches `value` times
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / pk["bf16_tflops"], "traffic": FWD_KERNEL_DRAM_TRAFFIC_BYTES,
-                     "traffic_source": "scaled_from_capture (attention kernel, batch-2 ncu capture x 2)",
+                     "traffic_source": "from_capture (attention kernel, ncu capture of this workload; algorithmic 335.5 MB)",
                      "peak_kind": f"{pk_kind} cuBLAS bf16 burst",
                      "kernel": "rope_prepass_kernel<bf16,128> + fwd_pair_kernel<bf16,causal> (two query heads of a KV group per CTA; one step = both launches)",
                      "step_ms": ms_step, "frac_of_nominal_2250": per_gpu / 2250.0,
