@@ -326,3 +326,21 @@ def test_two_heads_per_cta_lse_and_offset():
     Qc = Q[:, :, off:off + nq].contiguous()
     got = causal(Qc.to(DEV), K.to(DEV), V.to(DEV), q_offset=off, family=_lib.AF_FAMILY_TCGEN05)
     assert_close(got, orc.attention(Qc, K, V, causal=True, q_offset=off), torch.bfloat16, what="paired chunk")
+
+
+@pytest.mark.parametrize("variant", ["dense", "causal", "causal_alibi"])
+@pytest.mark.parametrize("case", [(3, 12, 4, 700, 128), (2, 8, 2, 900, 128), (3, 6, 6, 700, 64), (2, 6, 2, 520, 128)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_item_order_in_l2_sized_chunks(variant, case, monkeypatch):
+    """Problems whose K and V exceed the L2 are dealt out in chunks of (batch, head) units, odd
+    chunks with their rows of query tiles reversed.  A budget of a quarter megabyte forces many
+    chunks on a small problem: same results as the plain order, on both forward schedules (groups
+    of 3, 4 and 1 heads: pairs, one head per CTA, head dim 64)."""
+    B, Hq, Hkv, N, D = case
+    Q, K, V = qkv(6100 + N, B, Hq, Hkv, N, N, D, torch.bfloat16)
+    monkeypatch.setenv("ATTNFUSE_L2_KV_MB", "0.25")
+    chunked, want = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05)
+    monkeypatch.setenv("ATTNFUSE_L2_KV_MB", "1000000")
+    plain, _ = run_variant(variant, Q, K, V, _lib.AF_FAMILY_TCGEN05)
+    assert_close(chunked, want, torch.bfloat16, what=f"chunked item order {variant}")
+    assert torch.equal(chunked, plain)   # the order of the items does not change what an item computes
