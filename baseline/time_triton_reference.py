@@ -7,8 +7,8 @@ recipe (benchmarks/bench_runner.py:118-140): warm-up calls, then one CUDA-event 
 median.  With ``--impl ours`` the same cases run through this repository's package instead, with
 the same harness, so the two columns are comparable.
 
-    python baseline/time_triton_reference.py --out gpurun_out/triton_reference.jsonl
-    python baseline/time_triton_reference.py --impl ours --out gpurun_out/triton_ours.jsonl
+    python baseline/time_triton_reference.py --out triton_reference.jsonl
+    python baseline/time_triton_reference.py --impl ours --out triton_ours.jsonl
 """
 from __future__ import annotations
 
