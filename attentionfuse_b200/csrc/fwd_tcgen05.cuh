@@ -882,15 +882,34 @@ fwd_tcgen05_kernel(const TcArgs args, const __grid_constant__ CUtensorMap tmap_q
       }
       if (SPLIT) {
         // split-K decode: un-normalised partial of this (split, batch, head) for the combine kernel
-        if (row < p.N_q) {
-          const int64_t wr = ((int64_t)it.split * p.B + b) * ((int64_t)p.H_q * p.N_q) + (int64_t)h * p.N_q + row;
-          float4* dst = reinterpret_cast<float4*>(args.ws_acc + wr * D + half * (D / 2));
+        // The fp32 rows go through the warp's staging region too, 32 columns at a time, and leave
+        // as whole 128-byte lines (four rows per store instruction) instead of 32 lines per
+        // instruction: rows of the partials are D floats apart and consecutive in the workspace.
+        const int64_t wr0 = ((int64_t)it.split * p.B + b) * ((int64_t)p.H_q * p.N_q) + (int64_t)h * p.N_q + m0 + (warp & 3) * 32;
+        const uint32_t stage = sO + (uint32_t)((half * 4 + (warp & 3)) * 32 * 128);
+        const int rows_valid = min(32, p.N_q - (m0 + (warp & 3) * 32));   // rows of this warp that exist
 #pragma unroll
-          for (int q4 = 0; q4 < D / 8; ++q4) dst[q4] = make_float4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
-          if (half == 0) {
-            args.ws_m[wr] = m_all * kLn2;      // -inf when the split saw no key
-            args.ws_l[wr] = l_sum;
+        for (int part = 0; part < D / 64; ++part) {                       // 32 of the thread's D/2 columns per pass
+          __syncwarp();
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8)
+            sts128(stage + (uint32_t)(lane * 128 + ((c8 ^ (lane & 7)) << 4)),
+                   make_uint4(__float_as_uint(o[part * 32 + c8 * 4]), __float_as_uint(o[part * 32 + c8 * 4 + 1]),
+                              __float_as_uint(o[part * 32 + c8 * 4 + 2]), __float_as_uint(o[part * 32 + c8 * 4 + 3])));
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), c8 = lane & 7;
+            if (r < rows_valid) {
+              const uint4 v = lds128(stage + (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4)));
+              *reinterpret_cast<uint4*>(args.ws_acc + (wr0 + r) * D + half * (D / 2) + part * 32 + c8 * 4) = v;
+            }
           }
+        }
+        if (half == 0 && row < p.N_q) {
+          const int64_t wr = wr0 + lane;
+          args.ws_m[wr] = m_all * kLn2;      // -inf when the split saw no key
+          args.ws_l[wr] = l_sum;
         }
       } else {
         // The rows go out through shared memory: a thread owns one row, so direct stores touch 32
