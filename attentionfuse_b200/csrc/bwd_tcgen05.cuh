@@ -300,6 +300,9 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
     if (lane == 0) {
       tma_prefetch_desc(&map_a1); tma_prefetch_desc(&map_a2); tma_prefetch_desc(&map_b1); tma_prefetch_desc(&map_b2);
     }
+    // L2 hints: the stationary tiles are read once per item, the streamed rows once per stationary
+    // tile of their unit
+    const uint64_t pol_once = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
     BItem bi;
     int it0 = 0, qi = 0;
     bool ok = true;
@@ -313,8 +316,8 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
         const int ha = KVS ? h_kv : hx;
 #pragma unroll
         for (int pn = 0; pn < C::PANELS; ++pn) {
-          tma_load_4d(smem + pn * C::STAT_PANEL, &map_a1, &bars->stat_full, pn * 64, t0, ha, b);
-          tma_load_4d(smem + C::STAT_TILE + pn * C::STAT_PANEL, &map_a2, &bars->stat_full, pn * 64, t0, ha, b);
+          tma_load_4d_hint(smem + pn * C::STAT_PANEL, &map_a1, &bars->stat_full, pn * 64, t0, ha, b, pol_once);
+          tma_load_4d_hint(smem + C::STAT_TILE + pn * C::STAT_PANEL, &map_a2, &bars->stat_full, pn * 64, t0, ha, b, pol_once);
         }
       }
       int it = it0;                                                   // running step count
@@ -333,8 +336,8 @@ bwd_tcgen05_kernel(const BwdArgs args, const __grid_constant__ CUtensorMap map_a
             mbar_expect_tx(&bars->strm_full[st], 2 * C::STRM_TILE);
 #pragma unroll
             for (int pn = 0; pn < C::PANELS; ++pn) {
-              tma_load_4d(stage + pn * C::STRM_PANEL, &map_b1, &bars->strm_full[st], pn * 64, r0, hb, b);
-              tma_load_4d(stage + C::STRM_TILE + pn * C::STRM_PANEL, &map_b2, &bars->strm_full[st], pn * 64, r0, hb, b);
+              tma_load_4d_hint(stage + pn * C::STRM_PANEL, &map_b1, &bars->strm_full[st], pn * 64, r0, hb, b, pol_keep);
+              tma_load_4d_hint(stage + C::STRM_TILE + pn * C::STRM_PANEL, &map_b2, &bars->strm_full[st], pn * 64, r0, hb, b, pol_keep);
             }
           }
           if (KVS) {
