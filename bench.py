@@ -705,12 +705,15 @@ def sweep(which: str):
                     # split-K kernels, the mask as a range of keys, RoPE on the tiles in shared memory
                     cos, sin = (t.to(dev) for t in orc.build_rope_cache(L, D, 500000.0, dt))
                     pos = lens - 1
+                    ws_split = decode_workspace(S, B, Hq, D, dev)
                     for name, mask_kind, window, rope in (("causal", 1, 0, False), ("window4096", 2, 4096, False),
                                                           ("causal+rope", 1, 0, True)):
+                        # the rotated row takes the split grid, as the public call does by default
+                        row_ws, row_sched = (ws_split, dict(num_splits=S)) if rope else (ws, sched)
                         def step_masked():
                             Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
                             run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens,
-                                             workspace=ws, q_positions=pos, **sched, mask_kind=mask_kind, window=window,
+                                             workspace=row_ws, q_positions=pos, **row_sched, mask_kind=mask_kind, window=window,
                                              cos=cos if rope else None, sin=sin if rope else None)
                         ms = _median_ms(step_masked)
                         keys = float(torch.clamp(lens, max=window).sum().item()) if mask_kind == 2 else float(lens.sum().item())
