@@ -225,7 +225,7 @@ __device__ __forceinline__ void decode_segment(const AfDecodeParams& a, unsigned
     const int slot = tile % DEC_STAGES;
     const uint32_t kt = smem_u32(sK + slot * TILE_BYTES);
     const uint32_t vt = smem_u32(sV + slot * TILE_BYTES);
-    if (ROPE) {
+    if (ROPE && a.rope == 1) {   // rope == 2: the cache already holds rotated keys
       // rotate the K tile in place: a thread takes pairs of 16-byte chunks (c, c + CHUNKS/2) of a row
       const int key0 = lo + tile * DEC_BN;
       for (int i = tid; i < DEC_BN * (CHUNKS / 2); i += DEC_THREADS) {
@@ -879,6 +879,7 @@ int launch_decode_split(const AfDecodeParams& a, cudaStream_t st) {
   AF_REQUIRE(a.mask_kind == AF_MASK_FULL || a.mask_kind == AF_MASK_CAUSAL || (a.mask_kind == AF_MASK_WINDOW && a.window > 0),
              "decode takes full, causal or window masks (mask_kind %d, window %d)", a.mask_kind, a.window);
   if (a.rope) {
+    AF_REQUIRE(a.rope == 1 || a.rope == 2, "decode rope is 0, 1 (rotate query and keys) or 2 (query only), got %d", a.rope);
     AF_REQUIRE(a.cos && a.sin, "RoPE decode needs cos and sin tables");
     AF_REQUIRE(a.rope_stride_n % 8 == 0 && ((uintptr_t)a.cos & 15) == 0 && ((uintptr_t)a.sin & 15) == 0,
                "cos/sin rows must be 16-byte aligned");

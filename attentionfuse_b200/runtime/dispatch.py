@@ -195,7 +195,8 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
                   sin: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                   save_lse: Optional[torch.Tensor] = None, *, alibi_slopes=None,
                   kv_lens: Optional[torch.Tensor] = None, family: Optional[int] = None,
-                  q_offset: Optional[int] = None, keep_workspace: Optional[list] = None) -> torch.Tensor:
+                  q_offset: Optional[int] = None, keep_workspace: Optional[list] = None,
+                  kv_rotated: bool = False) -> torch.Tensor:
     """Run the fused forward; returns O with Q's shape and dtype.
 
     Extensions over the reference signature (all keyword-only): ``alibi_slopes`` overrides the
@@ -204,6 +205,9 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
     places query row 0 at that position of the key axis (chunked prefill against a cache: row
     i is masked, biased and rotated as position ``q_offset + i``), which also lifts the
     reference's restriction of masked graphs to N_q == N_kv (attnfuse/runtime/dispatch.py:140-148).
+    ``kv_rotated=True`` (positioned single-row decode of a RoPE graph) says that the cache already
+    holds rotated keys, as a serving stack stores them: only the query row is rotated, at its
+    position, and the step stays bandwidth-bound.  Anywhere else it is refused.
     """
     validate_qkv(Q, K, V)
     N_q, N_kv = Q.shape[2], K.shape[2]
@@ -235,7 +239,10 @@ def run_attention(graph: Graph, Q: torch.Tensor, K: torch.Tensor, V: torch.Tenso
         return run_flash_decode(graph, Q, K, V, bundle.sm_scale, bundle.bias_kind, K.shape[1], out,
                                 kv_lens=kv_lens, alibi_slopes=alibi_slopes, q_positions=q_positions,
                                 q_position=q_offset, mask_kind=bundle.mask_kind, window=bundle.window,
-                                cos=c, sin=s)
+                                cos=c, sin=s, kv_rotated=kv_rotated)
+    if kv_rotated:
+        raise ValueError("kv_rotated applies to the positioned single-row decode of a RoPE graph only "
+                         "(query length 1 with q_offset, f16/bf16, head_dim 64/128, N_kv >= 256)")
     if q_positions is not None:
         raise ValueError("per-sequence query positions are only supported on the flash-decoding path "
                          "(query length 1, f16/bf16, head_dim 64/128, N_kv >= 256)")

@@ -96,7 +96,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      num_splits: Optional[int] = None, workspace=None, exchange=None, exchange_mode: int = 0,
                      mask_kind: int = 0, window: int = 0, q_position: Optional[int] = None,
                      cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
-                     balanced_ctas: int = 0) -> torch.Tensor:
+                     balanced_ctas: int = 0, kv_rotated: bool = False) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
     when only the packed partial is requested)."""
     lib = _lib.load()
@@ -105,8 +105,9 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     if V.stride() != K.stride() and (V.stride(3) != 1 or any(s % 8 for s in V.stride()[:3])):
         V = V.contiguous()
     # A rotated row (cos / sin given) is bound by the rotation of the K tiles, not by bandwidth, and
-    # wants the higher occupancy of the split grid (0.60 against 1.2 ms at B16 H32/8 L32768).
-    if not balanced_ctas and num_splits is None and workspace is None and cos is None:
+    # wants the higher occupancy of the split grid (0.60 against 1.2 ms at B16 H32/8 L32768) --
+    # unless the cache already holds rotated keys (kv_rotated): then only the query row is rotated.
+    if not balanced_ctas and num_splits is None and workspace is None and (cos is None or kv_rotated):
         dev_index = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
         balanced_ctas = default_balanced_ctas(B, H_q, H_kv, N_kv, dev_index)
     if balanced_ctas:
@@ -134,7 +135,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     # copied afterwards: a decode step at short caches is bound by this call path
     key = (Q.dtype, Q.shape, Q.stride(), K.shape, K.stride(), V.stride(), None if out is None else out.stride(),
            float(sm_scale), int(bias_kind), int(num_splits), int(kv_offset), int(mask_kind), int(window or 0),
-           q_position, cos is not None and cos.stride(0), int(balanced_ctas))
+           q_position, cos is not None and cos.stride(0), int(balanced_ctas), bool(kv_rotated))
     template = _DECODE_TEMPLATES.get(key)
     if template is None:
         p = _lib.AfDecodeParams()
@@ -148,7 +149,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         if q_position is not None:
             p.q_position_p1 = int(q_position) + 1
         if cos is not None:
-            p.rope, p.rope_stride_n = 1, cos.stride(0)
+            p.rope, p.rope_stride_n = (2 if kv_rotated else 1), cos.stride(0)
         if out is not None:
             p.o_stride = _lib.strides(out)
         if len(_DECODE_TEMPLATES) >= 256:

@@ -707,14 +707,14 @@ def sweep(which: str):
                     pos = lens - 1
                     ws_split = decode_workspace(S, B, Hq, D, dev)
                     for name, mask_kind, window, rope in (("causal", 1, 0, False), ("window4096", 2, 4096, False),
-                                                          ("causal+rope", 1, 0, True)):
-                        # the rotated row takes the split grid, as the public call does by default
-                        row_ws, row_sched = (ws_split, dict(num_splits=S)) if rope else (ws, sched)
+                                                          ("causal+rope", 1, 0, True), ("causal+rope, rotated cache", 1, 0, 2)):
+                        # keys rotated on load take the split grid, as the public call does by default
+                        row_ws, row_sched = (ws_split, dict(num_splits=S)) if rope is True else (ws, sched)
                         def step_masked():
                             Kc, Vc = caches[it[0] % n_buf]; it[0] += 1
                             run_flash_decode(None, Q, Kc, Vc, 1.0 / D ** 0.5, 0, Hkv, out, kv_lens=lens,
                                              workspace=row_ws, q_positions=pos, **row_sched, mask_kind=mask_kind, window=window,
-                                             cos=cos if rope else None, sin=sin if rope else None)
+                                             cos=cos if rope else None, sin=sin if rope else None, kv_rotated=(rope == 2))
                         ms = _median_ms(step_masked)
                         keys = float(torch.clamp(lens, max=window).sum().item()) if mask_kind == 2 else float(lens.sum().item())
                         nb = 2.0 * Hkv * D * 2 * keys + 2.0 * B * Hq * D * 2

@@ -158,7 +158,9 @@ typedef struct AfDecodeParams {
    * kv_offset + (valid keys) - 1.
    * ALiBi measures its distance from there; AF_MASK_CAUSAL keeps keys at positions <= q_pos,
    * AF_MASK_WINDOW keys with |q_pos - position| < window; rope = 1 rotates the query at q_pos
-   * and every key at its own position (rotate-half, tables as in AfProblem) before the dot.
+   * and every key at its own position (rotate-half, tables as in AfProblem) before the dot;
+   * rope = 2 rotates the query only: the cache holds keys that were rotated when they were
+   * written (what a serving stack stores), and the step stays bandwidth-bound.
    * None of these exists in the reference, whose decode path takes dense and ALiBi graphs
    * only (attnfuse/runtime/flash_decode.py:46-65).  Zero-initialised fields give the
    * reference's behaviour. */

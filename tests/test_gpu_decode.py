@@ -153,6 +153,34 @@ def test_ragged_batch_decodes_with_rotation_at_each_sequence_end():
         assert_close(got[b:b + 1], want, dtype, what=f"ragged rope row {b}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_cache_of_rotated_keys_rotates_the_query_row_only(dtype):
+    """A serving cache holds keys that were rotated when they were written: `kv_rotated=True`
+    rotates the query row alone, at its position.  Same result as rotating the stored keys on
+    load (both round the rotated key to the cache type once), and the oracle's."""
+    from attentionfuse_b200.rope_utils import apply_rope
+    B, Hq, Hkv, L, D = 3, 16, 4, 3000, 128
+    Q, K, V = qkv(1850, B, Hq, Hkv, 1, L, D, dtype)
+    lens = lens_for(79, B, L)
+    cos, sin = orc.build_rope_cache(L, D, 500000.0, dtype)
+
+    @af.attention
+    def fn(Q, K, V):
+        return af.softmax(af.causal(af.rope(Q, K))) @ V
+
+    kw = dict(cos=cos.to(DEV), sin=sin.to(DEV), kv_lens=lens.to(DEV), q_offset=(lens - 1).to(DEV))
+    on_load = fn(Q.to(DEV), K.to(DEV), V.to(DEV), **kw)
+    K_rot = apply_rope(K.to(DEV).float(), cos.to(DEV).float(), sin.to(DEV).float()).to(dtype)   # fp32 math, one rounding
+    stored = fn(Q.to(DEV), K_rot, V.to(DEV), kv_rotated=True, **kw)
+    assert (stored.float() - on_load.float()).abs().max().item() <= 4e-3
+    for b in range(B):
+        n = int(lens[b])
+        want = orc.attention(Q[b:b + 1], K[b:b + 1, :, :n], V[b:b + 1, :, :n], causal=True, cos=cos, sin=sin, q_offset=n - 1)
+        assert_close(stored[b:b + 1], want, dtype, what=f"rotated cache row {b}")
+    with pytest.raises(ValueError):
+        fn(Q.to(DEV).expand(B, Hq, 4, D).contiguous(), K_rot[:, :, :4], V.to(DEV)[:, :, :4], cos=cos.to(DEV), sin=sin.to(DEV), kv_rotated=True)
+
+
 @pytest.mark.parametrize("splits", [1, 2, 7, 16])
 def test_split_counts_agree(splits):
     B, Hq, Hkv, L, D = 2, 32, 8, 2048, 128
