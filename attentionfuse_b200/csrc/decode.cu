@@ -121,6 +121,21 @@ struct XLayout {
   __device__ int64_t flag_off() const { return 2 * o_floats + 2 * lse_floats; }
 };
 
+// Position of local key j on the key axis (contiguous shard, or blocks dealt round-robin).
+__device__ __forceinline__ int key_pos(const AfDecodeParams& a, int j) {
+  if (a.kv_pos_block <= 0) return a.kv_offset + j;
+  const int blk = j / a.kv_pos_block;
+  return a.kv_offset + blk * a.kv_pos_stride + (j - blk * a.kv_pos_block);
+}
+// Number of local keys at positions <= pos (positions grow with the local index in both layouts).
+__device__ __forceinline__ int keys_upto(const AfDecodeParams& a, int pos) {
+  const int rel = pos - a.kv_offset;
+  if (rel < 0) return 0;
+  if (a.kv_pos_block <= 0) return rel + 1;
+  const int full = rel / a.kv_pos_stride, rem = rel - full * a.kv_pos_stride;
+  return full * a.kv_pos_block + min(rem + 1, a.kv_pos_block);
+}
+
 // One segment of split-K work: the query heads of chunk `chunk` of KV head (b, h_kv) against the
 // keys [lo, hi) of that head, written as un-normalised partials (m, l, acc) to the rows starting
 // at `ws_rowc` (the row of the chunk's first head).  Ends with a CTA barrier, so that segments
@@ -231,7 +246,7 @@ __device__ __forceinline__ void decode_segment(const AfDecodeParams& a, unsigned
       for (int i = tid; i < DEC_BN * (CHUNKS / 2); i += DEC_THREADS) {
         const int r = i / (CHUNKS / 2), c = i - r * (CHUNKS / 2);
         if (key0 + r >= hi) continue;
-        const int64_t tab = (int64_t)(a.kv_offset + key0 + r) * a.rope_stride_n + c * 8;
+        const int64_t tab = (int64_t)key_pos(a, key0 + r) * a.rope_stride_n + c * 8;
         const uint4 cl = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.cos) + tab));
         const uint4 ch = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.cos) + tab + D / 2));
         const uint4 sl = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.sin) + tab));
@@ -277,7 +292,7 @@ __device__ __forceinline__ void decode_segment(const AfDecodeParams& a, unsigned
         const int key = key_base + j * 8 + 2 * t + (e & 1);
         const int row = e >> 1;
         float x = s[j][e] * scale2;
-        if (a.bias_kind == AF_BIAS_ALIBI) x -= slope2[row] * (float)abs(q_pos - (a.kv_offset + key));
+        if (a.bias_kind == AF_BIAS_ALIBI) x -= slope2[row] * (float)abs(q_pos - key_pos(a, key));
         x = key < hi ? x : -INFINITY;
         s[j][e] = x;
         mx[row] = fmaxf(mx[row], x);
@@ -404,12 +419,12 @@ struct KeyRange { int lo, span, q_pos; };
 __device__ __forceinline__ KeyRange key_range(const AfDecodeParams& a, int b) {
   const int len_b = a.kv_lens ? min(max(a.kv_lens[b], 0), a.N_kv) : a.N_kv;
   KeyRange r;
-  r.q_pos = a.q_positions ? a.q_positions[b] : (a.q_position_p1 > 0 ? a.q_position_p1 - 1 : a.kv_offset + len_b - 1);
+  r.q_pos = a.q_positions ? a.q_positions[b] : (a.q_position_p1 > 0 ? a.q_position_p1 - 1 : key_pos(a, len_b - 1));
   int k_lo = 0, k_hi = len_b;
-  if (a.mask_kind == AF_MASK_CAUSAL) k_hi = min(k_hi, r.q_pos - a.kv_offset + 1);
+  if (a.mask_kind == AF_MASK_CAUSAL) k_hi = min(k_hi, keys_upto(a, r.q_pos));
   if (a.mask_kind == AF_MASK_WINDOW) {
-    k_lo = max(0, r.q_pos - a.window + 1 - a.kv_offset);
-    k_hi = min(k_hi, r.q_pos + a.window - a.kv_offset);
+    k_lo = keys_upto(a, r.q_pos - a.window);
+    k_hi = min(k_hi, keys_upto(a, r.q_pos + a.window - 1));
   }
   r.lo = k_lo;
   r.span = max(k_hi - k_lo, 0);

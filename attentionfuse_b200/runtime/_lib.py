@@ -87,6 +87,7 @@ class AfDecodeParams(C.Structure):
         ("mask_kind", I32), ("window", I32), ("rope", I32), ("q_position_p1", I32),
         ("cos", PTR), ("sin", PTR), ("rope_stride_n", I64),
         ("balanced_ctas", I32),
+        ("kv_pos_block", I32), ("kv_pos_stride", I32),
     ]
 
 

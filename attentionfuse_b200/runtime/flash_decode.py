@@ -96,7 +96,8 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
                      num_splits: Optional[int] = None, workspace=None, exchange=None, exchange_mode: int = 0,
                      mask_kind: int = 0, window: int = 0, q_position: Optional[int] = None,
                      cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
-                     balanced_ctas: int = 0, kv_rotated: bool = False) -> torch.Tensor:
+                     balanced_ctas: int = 0, kv_rotated: bool = False,
+                     kv_pos_block: int = 0, kv_pos_stride: int = 0) -> torch.Tensor:
     """Two launches: split-K partials, then the LSE combine.  Returns `out` (or `partial`
     when only the packed partial is requested)."""
     lib = _lib.load()
@@ -135,7 +136,8 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
     # copied afterwards: a decode step at short caches is bound by this call path
     key = (Q.dtype, Q.shape, Q.stride(), K.shape, K.stride(), V.stride(), None if out is None else out.stride(),
            float(sm_scale), int(bias_kind), int(num_splits), int(kv_offset), int(mask_kind), int(window or 0),
-           q_position, cos is not None and cos.stride(0), int(balanced_ctas), bool(kv_rotated))
+           q_position, cos is not None and cos.stride(0), int(balanced_ctas), bool(kv_rotated),
+           int(kv_pos_block), int(kv_pos_stride))
     template = _DECODE_TEMPLATES.get(key)
     if template is None:
         p = _lib.AfDecodeParams()
@@ -145,6 +147,7 @@ def run_flash_decode(graph: Optional[Graph], Q: torch.Tensor, K: torch.Tensor, V
         p.q_stride, p.k_stride, p.v_stride = _lib.strides(Q), _lib.strides(K), _lib.strides(V)
         p.kv_offset = int(kv_offset)
         p.balanced_ctas = int(balanced_ctas)
+        p.kv_pos_block, p.kv_pos_stride = int(kv_pos_block), int(kv_pos_stride)
         p.mask_kind, p.window = int(mask_kind), int(window or 0)
         if q_position is not None:
             p.q_position_p1 = int(q_position) + 1

@@ -199,8 +199,6 @@ class ShardedDecodePlan:
         if kv_lens is None:
             kv_lens = torch.full((B,), L_total, dtype=torch.int32)
         if layout == "cyclic":
-            if bias_kind != 0:
-                raise NotImplementedError("ALiBi needs key positions: use the contiguous layout")
             if L_total % (world * CYCLIC_BLOCK):
                 raise ValueError(f"cyclic layout needs L a multiple of {world * CYCLIC_BLOCK}")
             self.lo, self.hi = 0, L_total // world
@@ -213,7 +211,10 @@ class ShardedDecodePlan:
         self.q_positions = (kv_lens.to(torch.int32) - 1).to(device) if bias_kind == 1 else None
         self.slopes = None if slopes is None else slopes.to(device=device, dtype=dtype).contiguous()
         index = device.index if getattr(device, "index", None) is not None else torch.cuda.current_device()
-        self.kv_offset = self.lo if layout == "contiguous" else 0
+        # position of local key j: lo + j (contiguous) or rank * block + (j / block) * world * block +
+        # j % block (cyclic), so that ALiBi distances are measured on the true key axis
+        self.kv_offset = self.lo if layout == "contiguous" else rank * CYCLIC_BLOCK
+        self.kv_pos = dict(kv_pos_block=CYCLIC_BLOCK, kv_pos_stride=world * CYCLIC_BLOCK) if layout == "cyclic" else {}
         self.num_splits = _pick_num_splits(B, H_q, H_kv, max(self.hi - self.lo, 1), index, kv_lens is not None)
         self.balanced_ctas = 0
         rows = None
@@ -256,7 +257,7 @@ class ShardedDecodePlan:
                              kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
                              q_positions=self.q_positions, num_splits=self.num_splits,
                              workspace=self.workspace, exchange=self.exchange, exchange_mode=3,
-                             balanced_ctas=self.balanced_ctas)
+                             balanced_ctas=self.balanced_ctas, **self.kv_pos)
             return out
         if self.exchange is not None:
             # two launches of the local decode (split, combine + push to all peers) and the
@@ -264,12 +265,12 @@ class ShardedDecodePlan:
             run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, None,
                              kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
                              q_positions=self.q_positions, num_splits=self.num_splits,
-                             workspace=self.workspace, exchange=self.exchange)
+                             workspace=self.workspace, exchange=self.exchange, **self.kv_pos)
             return self.exchange.wait_merge(out)
         run_flash_decode(None, Q, K_local, V_local, self.sm_scale, self.bias_kind, self.H_kv, None,
                          kv_lens=self.lens_local, alibi_slopes=self.slopes, kv_offset=self.kv_offset,
                          q_positions=self.q_positions, partial=self.partial, num_splits=self.num_splits,
-                         workspace=self.workspace)
+                         workspace=self.workspace, **self.kv_pos)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered.view(-1, *self.partial.shape[1:]), self.partial,
                                         group=self.group)

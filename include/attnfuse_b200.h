@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define AF_ABI_VERSION 3
+#define AF_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define AF_API __attribute__((visibility("default")))
@@ -175,6 +175,12 @@ typedef struct AfDecodeParams {
    * group = H_q / H_kv; num_splits is ignored.  The reference splits every sequence into the
    * same number of pieces (attnfuse/runtime/flash_decode.py:114-131). */
   int32_t balanced_ctas;
+  /* Block-cyclic KV sharding: with kv_pos_block > 0 local key j of this rank sits at position
+   * kv_offset + (j / kv_pos_block) * kv_pos_stride + j % kv_pos_block of the key axis (blocks of
+   * kv_pos_block keys dealt round-robin to the ranks: kv_offset = rank * block, kv_pos_stride =
+   * ranks * block), so that ALiBi, masks and rotation see true positions.  0: local key j sits at
+   * kv_offset + j (contiguous shard). */
+  int32_t kv_pos_block, kv_pos_stride;
 } AfDecodeParams;
 
 /* Replaces the forward launch in run_attention (attnfuse/runtime/dispatch.py:196-214)

@@ -26,7 +26,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert sorted(_lib.EXPORTS) == names
-    assert lib.af_abi_version() == 3
+    assert lib.af_abi_version() == 4
     assert lib.af_launch_count() >= 0
 
 
@@ -36,9 +36,9 @@ def test_struct_layouts_match_the_header(tmp_path):
         '#include <stdio.h>\n#include <stddef.h>\n#include "attnfuse_b200.h"\n'
         "int main(void) {\n"
         '  printf("%zu %zu %zu %zu\\n", sizeof(AfProblem), sizeof(AfFwdParams), sizeof(AfBwdParams), sizeof(AfDecodeParams));\n'
-        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", offsetof(AfProblem, q), offsetof(AfProblem, status), offsetof(AfFwdParams, workspace),\n'
+        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", offsetof(AfProblem, q), offsetof(AfProblem, status), offsetof(AfFwdParams, workspace),\n'
         "         offsetof(AfBwdParams, dv), offsetof(AfDecodeParams, partial), offsetof(AfProblem, q_bits),\n"
-        "         offsetof(AfBwdParams, dq_accum), offsetof(AfDecodeParams, balanced_ctas));\n"
+        "         offsetof(AfBwdParams, dq_accum), offsetof(AfDecodeParams, balanced_ctas), offsetof(AfDecodeParams, kv_pos_stride));\n"
         "  return 0;\n}\n")
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-std=c99", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
@@ -48,7 +48,7 @@ def test_struct_layouts_match_the_header(tmp_path):
                          C.sizeof(_lib.AfDecodeParams)]
     assert sizes[4:] == [_lib.AfProblem.q.offset, _lib.AfProblem.status.offset, _lib.AfFwdParams.workspace.offset,
                          _lib.AfBwdParams.dv.offset, _lib.AfDecodeParams.partial.offset, _lib.AfProblem.q_bits.offset,
-                         _lib.AfBwdParams.dq_accum.offset, _lib.AfDecodeParams.balanced_ctas.offset]
+                         _lib.AfBwdParams.dq_accum.offset, _lib.AfDecodeParams.balanced_ctas.offset, _lib.AfDecodeParams.kv_pos_stride.offset]
 
 
 def test_host_only_entry_points():

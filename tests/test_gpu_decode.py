@@ -247,6 +247,35 @@ def test_sharded_plan_layouts_emulated(world, layout):
         assert (per_rank.max(0).values - per_rank.min(0).values).max().item() <= 256   # balanced to one block
 
 
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("layout", ["contiguous", "cyclic"])
+def test_sharded_plan_with_alibi_sees_true_key_positions(world, layout):
+    """ALiBi measures the distance of every key from the query row on the true key axis: a rank of
+    the block-cyclic layout passes its rank offset and the block / stride of the dealing
+    (AfDecodeParams.kv_pos_block / kv_pos_stride), a contiguous shard its first position."""
+    from attentionfuse_b200.runtime.flash_decode import run_flash_decode as rfd
+    B, Hq, Hkv, L, D = 3, 16, 4, 4096, 128
+    Q, K, V = qkv(1995, B, Hq, Hkv, 1, L, D, torch.bfloat16)
+    lens = torch.tensor([4096, 2049, 700], dtype=torch.int32)
+    slopes = _alibi_slopes(Hq, "cpu", "torch.bfloat16")
+    q, k, v = Q.to(DEV), K.to(DEV), V.to(DEV)
+    gathered = torch.empty(world, B, Hq, D + 1, dtype=torch.float32, device=DEV)
+    for r in range(world):
+        plan = ShardedDecodePlan(B, Hq, Hkv, D, L, r, world, lens, torch.device(DEV, 0), torch.bfloat16, layout=layout,
+                                 bias_kind=1, slopes=slopes)
+        if layout == "cyclic":
+            kl, vl = cyclic_slice(k, r, world).contiguous(), cyclic_slice(v, r, world).contiguous()
+        else:
+            kl, vl = k[:, :, plan.lo:plan.hi], v[:, :, plan.lo:plan.hi]
+        rfd(None, q, kl, vl, plan.sm_scale, 1, Hkv, None, kv_lens=plan.lens_local, alibi_slopes=plan.slopes,
+            kv_offset=plan.kv_offset, q_positions=plan.q_positions, partial=plan.partial, num_splits=plan.num_splits,
+            workspace=plan.workspace, **plan.kv_pos)
+        gathered[r].copy_(plan.partial)
+    out = torch.empty(B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    combine_gathered(gathered, out)
+    assert_close(out, orc.attention(Q, K, V, kv_lens=lens, slopes=slopes), torch.bfloat16, what=f"alibi {layout} world={world}")
+
+
 def _emulated_exchanges(world, B, Hq, D, wait_cycles=0):
     from attentionfuse_b200.runtime import _lib
     n = int(_lib.load().af_decode_exchange_bytes(world, B, Hq, D)) // 4
